@@ -1,0 +1,81 @@
+// Shared helpers of the sleuth_b200 kernels (sm_100a).
+//
+// Conventions of every exported launcher:
+//   * `extern "C" int slb_<name>(..., void* stream)`; returns 0, or a non-zero code after storing a
+//     message that `slb_last_error()` returns. A launcher checks every size it was given and refuses
+//     what its kernel cannot run; it never launches a kernel on sizes it has not checked.
+//   * activations and cache entries are `float` or `__nv_bfloat16` (the launcher's `dtype` argument:
+//     0 = float32, 1 = bfloat16); the residual stream, norm gains, biases, rotation tables and logits
+//     are always float32; all reductions accumulate in float32.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace slb {
+
+constexpr int kPageTokens = 64;   // tokens per cache page
+
+enum Dtype : int { kF32 = 0, kBF16 = 1 };
+
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+
+#define SLB_REQUIRE(cond, ...)                    \
+  do {                                            \
+    if (!(cond)) return slb::fail(1, __VA_ARGS__); \
+  } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+// The order of additions is fixed by the thread layout, so a row's sum never depends on what else runs.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// 8 bfloat16 values in one 16-byte register group.
+struct alignas(16) Bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+}  // namespace slb

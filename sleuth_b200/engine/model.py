@@ -1,0 +1,101 @@
+"""A model as the engine sees it: an embedding, layers built from a description, a schedule, a head.
+
+``Model`` knows nothing about any architecture. It builds each layer from its ``LayerSpec`` through
+the part registries, collects the tensors the parts declare under the names the description gives
+them, asks the parts what their cache entries must hold, and runs ``ModelSpec.schedule``: a list of
+layer applications that may name a layer twice (its weights are then shared and each application has
+a cache entry of its own, as the reference's ``shared_layers``, sleuth/forge/model/config.py:80-86)
+or let an application read the cache entry an earlier one wrote.
+
+One forward pass is the reference's ``Transformer.forward`` (sleuth/forge/model/transformer.py:257-313)
+for a ragged batch: embed, run the layers on the float32 stream, final norm and output matrix on the
+rows whose logits are wanted only.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..parts.base import BuildContext, ParamDecl, build_layer
+from ..parts.ends import LMHead, TokenEmbedding
+from ..parts.spec import ModelSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, ctx: BuildContext):
+        self.spec, self.ctx = spec, ctx
+        self.embedding = TokenEmbedding(spec.embedding, ctx)
+        self.layers = [build_layer(ls, ctx) for ls in spec.layers]
+        self.head = LMHead(spec.head, ctx)
+        self.hidden = spec.embedding.dim
+        self.vocab = spec.head.vocab
+        # cache entries: the first application that names an entry owns it
+        self.entry_owner: dict[int, int] = {}
+        for i, e in enumerate(spec.schedule):
+            self.entry_owner.setdefault(e.cache, i)
+        self.cache_requests = [self.layers[spec.schedule[self.entry_owner[c]].layer].cache_request()
+                               for c in range(len(self.entry_owner))]
+
+    # ---- weights ----
+    def expected(self) -> dict[str, ParamDecl]:
+        out = {self.spec.embedding.name: self.embedding.declare()["weight"]}
+        for i, (layer, ls) in enumerate(zip(self.layers, self.spec.layers)):
+            for local, decl in layer.declare().items():
+                if local not in ls.names:
+                    raise KeyError(f"layer {i}: its description gives no checkpoint name for tensor {local!r}")
+                out[ls.names[local]] = decl
+        hd = self.head.declare()
+        out[self.spec.head.norm_name] = hd["norm.weight"]
+        if "weight" in hd:
+            out[self.spec.head.name] = hd["weight"]
+        return out
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.embedding.bind({"weight": tensors[self.spec.embedding.name]})
+        for layer, ls in zip(self.layers, self.spec.layers):
+            layer.bind({local: tensors[ls.names[local]] for local in layer.declare() if ls.names[local] in tensors})
+        head = {"norm.weight": tensors[self.spec.head.norm_name]}
+        if not self.spec.head.tied:
+            head["weight"] = tensors[self.spec.head.name]
+        self.head.bind(head, embedding_table=self.embedding.table)
+
+    # ---- one step ----
+    def forward(self, b, cache, ws, logits: torch.Tensor) -> torch.Tensor:
+        """Run the tokens of batch ``b``; fill ``logits`` [len(b.rows), vocab] (float32)."""
+        b.stream = torch.cuda.current_stream().cuda_stream   # inside a graph capture this is the capture stream
+        mark = ws.mark()
+        x = ws.take((b.T, self.hidden), torch.float32)
+        self.embedding.forward(b.token_ids, x, b.stream)
+        for i, e in enumerate(self.spec.schedule):
+            view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
+            self.layers[e.layer].forward(x, b, view, ws)
+        if logits.shape[0]:
+            self.head.forward(x, b.rows, logits, ws, b.stream)
+        ws.release(mark)
+        return logits
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for t in self._all_tensors():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def _all_tensors(self):
+        yield self.embedding.table
+        yield self.head.proj.weight
+        yield self.head.norm.weight
+        for layer in self.layers:
+            for part in getattr(layer, "children", {}).values():
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor):
+                        yield v
+                    elif hasattr(v, "weight") and isinstance(getattr(v, "weight"), torch.Tensor):
+                        yield v.weight
+
+
+def declare_model(spec: ModelSpec) -> dict[str, ParamDecl]:
+    """The tensors a model description expects, found without a GPU."""
+    ctx = BuildContext(device=torch.device("cpu"), dtype=torch.float32, max_positions=1)
+    return Model(spec, ctx).expected()

@@ -1,0 +1,197 @@
+"""The step function: run the tokens a batch brings, from the cache, and return the wanted logits.
+
+A step takes sequences that start together (their prompts, of unequal lengths) or go on together
+(one token each); in fact each sequence may bring any number of tokens, and they are appended after
+what its slot already holds. Only the given tokens are computed. Every sequence's keys and values go
+to its own pages and every query reads its own sequence's pages, so no padding exists and nothing a
+sequence computes depends on the others in the batch.
+
+The reference's counterpart is ``Transformer.forward(idx, cache)`` with one shared position for a
+rectangular batch and logits for every position (sleuth/forge/model/transformer.py:257-313,
+sleuth/forge/infer/kv_cache.py:34,62-64); ragged batches, per-sequence positions and logits at chosen
+rows only are this library's own.
+
+Long steps are cut into chunks of at most ``max_step_tokens`` tokens; a chunk runs through all
+layers before the next begins, so later chunks of a sequence find the earlier ones in the cache.
+A step in which every sequence brings one token is replayed as a CUDA graph from its second
+occurrence at a batch size on (the reference captures one decode step per length bucket,
+sleuth/forge/infer/cuda_graph.py:96-129; here lengths live in device tables, so one graph per batch
+size serves every length).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache.book import CacheFull
+from ..kernels import ops
+from ..parts.base import Workspace
+from .batch import MetaStager
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: object              # sequence of token ids
+    want: object = ()           # positions among ``tokens`` whose logits are wanted
+
+
+class Stepper:
+    def __init__(self, model, cache, device, max_len: int | None = None, max_step_tokens: int = 8192,
+                 use_graphs: bool = True, max_graph_batch: int = 256):
+        self.model, self.cache = model, cache
+        self.max_len = cache.book.max_len if max_len is None else min(int(max_len), cache.book.max_len)
+        self.device = torch.device(device)
+        self.max_step_tokens = max_step_tokens
+        self.use_graphs = use_graphs
+        self.max_graph_batch = max_graph_batch
+        self.ws = Workspace(self.device)
+        self.meta = MetaStager(self.device, cache.n_groups, cache.stride)
+        self._graphs: dict = {}
+        self._seen_decode: set = set()
+        self._decode_logits: torch.Tensor | None = None
+        self._graph_key = None
+        self.launch_count = 0
+        ops.lib()   # build or load the kernels now; fail here, loudly, if that is impossible
+
+    # ------------------------------------------------------------------ public ----
+    def step(self, entries: list[StepEntry], floats: np.ndarray | None = None) -> torch.Tensor:
+        """Run one step. Returns float32 logits ``[sum(len(e.want)), vocab]`` in the order of the
+        entries and of their ``want``. After a step of single tokens the result may be a view of a
+        buffer that the next step overwrites."""
+        if not entries:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
+        toks = [np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries]
+        book = self.cache.book
+        for e, t in zip(entries, toks):
+            if t.size == 0:
+                raise ValueError(f"slot {e.slot}: a step must bring at least one token for every sequence")
+            if t.min() < 0 or t.max() >= self.model.vocab:
+                raise ValueError(f"slot {e.slot}: token ids must lie in [0, {self.model.vocab})")
+            for w in e.want:
+                if not 0 <= int(w) < t.size:
+                    raise ValueError(f"slot {e.slot}: wanted position {w} is outside its {t.size} tokens")
+        slots = [int(e.slot) for e in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a step names a slot twice")
+        finals = [int(book.lengths[s]) + int(t.size) for s, t in zip(slots, toks)]
+        for s, n in zip(slots, finals):
+            if n > self.max_len:
+                raise CacheFull(f"slot {s} would hold {n} tokens; the longest sequence allowed is {self.max_len}")
+
+        if all(t.size == 1 for t in toks):
+            return self._decode(entries, slots, toks, floats)
+
+        n_want = sum(len(e.want) for e in entries)
+        out = torch.empty((n_want, self.model.vocab), dtype=torch.float32, device=self.device)
+        out_base, acc = [], 0
+        for e in entries:
+            out_base.append(acc)
+            acc += len(e.want)
+        done = [0] * len(entries)
+        while True:
+            chunk, room = [], self.max_step_tokens
+            for i, t in enumerate(toks):
+                left = t.size - done[i]
+                if left and room:
+                    take = min(left, room)
+                    chunk.append((i, done[i], take))
+                    room -= take
+            if not chunk:
+                break
+            self._run_chunk(entries, slots, toks, chunk, out, out_base)
+            for i, start, take in chunk:
+                done[i] = start + take
+        return out
+
+    # ------------------------------------------------------------------ chunks ----
+    def _run_chunk(self, entries, slots, toks, chunk, out, out_base) -> None:
+        book = self.cache.book
+        c_slots = [slots[i] for i, _, _ in chunk]
+        c_past = [int(book.lengths[s]) for s in c_slots]
+        c_counts = [take for _, _, take in chunk]
+        new_lens = [p + c for p, c in zip(c_past, c_counts)]
+        book.grow(c_slots, new_lens)
+        tokens = np.concatenate([toks[i][start:start + take] for i, start, take in chunk]).astype(np.int32)
+        rows, dest = [], []
+        base = 0
+        for i, start, take in chunk:
+            for j, w in enumerate(entries[i].want):
+                w = int(w)
+                if start <= w < start + take:
+                    rows.append(base + w - start)
+                    dest.append(out_base[i] + j)
+            base += take
+        order = np.argsort(np.asarray(dest, dtype=np.int64), kind="stable") if dest else np.zeros(0, dtype=np.int64)
+        rows_a = np.asarray(rows, dtype=np.int32)[order] if rows else np.zeros(0, dtype=np.int32)
+        dest_a = np.asarray(dest, dtype=np.int64)[order] if dest else np.zeros(0, dtype=np.int64)
+        b = self.meta.upload(c_slots, c_past, c_counts, tokens, rows_a, book.tables_for(c_slots))
+        W = rows_a.shape[0]
+        if W and np.array_equal(dest_a, np.arange(dest_a[0], dest_a[0] + W)):
+            self.model.forward(b, self.cache, self.ws, out[int(dest_a[0]):int(dest_a[0]) + W])
+        elif W:
+            mark = self.ws.mark()
+            tmp = self.ws.take((W, self.model.vocab), torch.float32)
+            self.model.forward(b, self.cache, self.ws, tmp)
+            out.index_copy_(0, torch.from_numpy(dest_a).to(self.device), tmp)
+            self.ws.release(mark)
+        else:
+            self.model.forward(b, self.cache, self.ws, out[:0])
+        book.commit(c_slots, new_lens)
+
+    # ------------------------------------------------------------------ decode ----
+    def _decode(self, entries, slots, toks, floats) -> torch.Tensor:
+        book = self.cache.book
+        n = len(slots)
+        past = [int(book.lengths[s]) for s in slots]
+        new_lens = [p + 1 for p in past]
+        book.grow(slots, new_lens)
+        tokens = np.asarray([int(t[0]) for t in toks], dtype=np.int32)
+        rows = np.arange(n, dtype=np.int32)
+        if floats is None:
+            floats = np.zeros(n, dtype=np.float32)
+        b = self.meta.upload(slots, past, [1] * n, tokens, rows, book.tables_for(slots), floats=floats)
+        self.last_batch = b
+        if self._decode_logits is None or self._decode_logits.shape[0] < n:
+            cap = max(n, 8 if self._decode_logits is None else 2 * self._decode_logits.shape[0])
+            self._decode_logits = torch.empty((cap, self.model.vocab), dtype=torch.float32, device=self.device)
+            self._graphs.clear()
+        logits = self._decode_logits[:n]
+
+        key = (self.ws.generation, self.meta.generation)
+        if key != self._graph_key:
+            self._graphs.clear()
+            self._graph_key = key
+        graph = self._graphs.get(n)
+        if graph is not None:
+            graph.replay()
+        elif self.use_graphs and n <= self.max_graph_batch and n in self._seen_decode:
+            self._graphs[n] = self._capture(b, logits)
+            key = (self.ws.generation, self.meta.generation)
+            self._graph_key = key
+            self._graphs[n].replay()
+        else:
+            self.model.forward(b, self.cache, self.ws, logits)
+            self._seen_decode.add(n)
+        book.commit(slots, new_lens)
+
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == n:
+            return logits
+        if not wanted:
+            return logits[:0]
+        return logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
+
+    def _capture(self, b, logits):
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        self.ws.frozen = True
+        try:
+            with torch.cuda.graph(g):
+                self.model.forward(b, self.cache, self.ws, logits)
+        finally:
+            self.ws.frozen = False
+        return g

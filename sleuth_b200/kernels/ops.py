@@ -1,0 +1,154 @@
+"""Thin, checked Python fronts of the CUDA launchers.
+
+Every function takes CUDA tensors, checks device, dtype, contiguity and the sizes that tie the
+arguments together, and launches on the stream it is given (an integer handle, the current torch
+stream by default). Nothing here computes with torch operations, with one exception that the
+architecture's own engine makes too: the bfloat16 matrix product of more rows than the skinny
+kernel takes is a library product (cuBLAS through ``torch.mm``), as the reference's ``nn.Linear``
+is (sleuth/forge/model/attention.py:106-108,157; mlp.py:38-41; transformer.py:302).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+
+DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def lib() -> library.KernelLibrary:
+    return library.load()
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None:
+            _need(t.is_cuda, "the kernels of sleuth_b200 run on CUDA tensors only")
+            _need(t.is_contiguous(), f"tensor of shape {tuple(t.shape)} must be contiguous")
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0, stream=None) -> None:
+    _cuda(ids, table, x)
+    T, d = x.shape
+    _need(ids.dtype == torch.int32 and ids.numel() >= T, "embed: ids must be int32, one per row of x")
+    _need(table.shape[1] == d and x.dtype == torch.float32 and table.dtype in DT, "embed: shapes or dtypes disagree")
+    lib().call("slb_embed", _p(ids), _p(table), DT[table.dtype], _p(x), T, d, float(scale),
+               stream if stream is not None else current_stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
+            stream=None) -> None:
+    _cuda(x, w, out, rows)
+    R, d = out.shape
+    _need(x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype in DT, "rmsnorm: dtypes")
+    _need(x.shape[1] == d and w.numel() == d, "rmsnorm: widths disagree")
+    if rows is None:
+        _need(x.shape[0] >= R, "rmsnorm: fewer input rows than output rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= R, "rmsnorm: rows must be int32, one per output row")
+    lib().call("slb_rmsnorm", _p(x), _p(w), _p(out), DT[out.dtype], _p(rows), R, d, float(eps),
+               stream if stream is not None else current_stream())
+
+
+def add(x: torch.Tensor, delta: torch.Tensor, stream=None) -> None:
+    _cuda(x, delta)
+    _need(x.dtype == torch.float32 and delta.dtype in DT and x.numel() == delta.numel(), "add: shapes or dtypes")
+    lib().call("slb_add", _p(x), _p(delta), DT[delta.dtype], x.numel(),
+               stream if stream is not None else current_stream())
+
+
+def swiglu(gu: torch.Tensor, act: torch.Tensor, stream=None) -> None:
+    _cuda(gu, act)
+    T, inter = act.shape
+    _need(gu.shape == (T, 2 * inter) and gu.dtype == act.dtype and act.dtype in DT, "swiglu: shapes or dtypes")
+    lib().call("slb_swiglu", _p(gu), _p(act), DT[act.dtype], T, inter,
+               stream if stream is not None else current_stream())
+
+
+def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table,
+             heads: int, kv_heads: int, head_dim: int, rot_dim: int, eps: float, stream=None) -> None:
+    _cuda(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
+    T = q_out.shape[0]
+    rows = heads + 2 * kv_heads
+    _need(qkv.shape == (T, rows * head_dim) and q_out.shape[1:] == (heads, head_dim), "qkv_post: shapes disagree")
+    _need(qkv.dtype == q_out.dtype and qkv.dtype in DT, "qkv_post: dtypes")
+    for v in (bias, q_gain, k_gain, cos, sin):
+        _need(v is None or v.dtype == torch.float32, "qkv_post: gains, biases and tables are float32")
+    _need(bias is None or bias.numel() == rows * head_dim, "qkv_post: bias length")
+    _need(q_gain is None or (q_gain.numel() == head_dim and k_gain.numel() == head_dim), "qkv_post: gain length")
+    if rot_dim:
+        _need(cos is not None and cos.shape[1] == rot_dim // 2 and sin.shape == cos.shape, "qkv_post: rotation tables")
+    stride = 0
+    if kv_heads and k_pool is not None:
+        _need(k_pool.dtype == qkv.dtype and k_pool.shape == v_pool.shape and
+              tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim), "qkv_post: cache pool shape or dtype")
+        _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "qkv_post: block table")
+        stride = block_table.shape[1]
+    _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "qkv_post: token tables are int32")
+    lib().call("slb_qkv_post", _p(qkv), _p(bias), _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(q_out), _p(k_pool),
+               _p(v_pool), _p(tok_seq), _p(tok_pos), _p(block_table), stride, T, heads, kv_heads, head_dim, rot_dim,
+               float(eps), DT[qkv.dtype], stream if stream is not None else current_stream())
+
+
+def attention(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, heads: int, kv_heads: int, head_dim: int,
+              window: int, scale: float, stream=None) -> None:
+    _cuda(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table)
+    T = q.shape[0]
+    _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
+    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype and q.dtype in DT, "attention: dtypes")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "attention: block table")
+    lib().call("slb_attention_generic", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(tok_seq), _p(tok_pos),
+               _p(block_table), block_table.shape[1], T, heads, kv_heads, head_dim, int(window), float(scale),
+               DT[q.dtype], stream if stream is not None else current_stream())
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, accumulate: bool = False,
+             stream=None) -> None:
+    """out[M, N] (+)= a[M, K] @ w[N, K]^T (+ bias), all float32, plain FMA."""
+    _cuda(a, w, out, bias)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm_f32: shapes disagree")
+    _need(a.dtype == w.dtype == out.dtype == torch.float32, "gemm_f32: float32 only")
+    lib().call("slb_gemm_f32", _p(a), _p(w), _p(bias), _p(out), M, N, K, K, K, N, int(accumulate),
+               stream if stream is not None else current_stream())
+
+
+def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:
+    _cuda(logits, recent, n_recent, banned, n_banned)
+    R = logits.shape[0]
+    lib().call("slb_penalize", _p(logits), logits.stride(0), R, limit, _p(recent), _p(n_recent),
+               0 if recent is None else recent.shape[1], float(penalty), _p(banned), _p(n_banned),
+               0 if banned is None else banned.shape[1], stream if stream is not None else current_stream())
+
+
+def argmax(logits: torch.Tensor, limit: int, out: torch.Tensor, stream=None) -> None:
+    _need(logits.is_cuda and out.is_cuda and logits.dtype == torch.float32 and out.dtype == torch.int32, "argmax: dtypes")
+    _need(logits.stride(1) == 1 and out.numel() >= logits.shape[0] and 0 < limit <= logits.shape[1], "argmax: shapes")
+    lib().call("slb_argmax", _p(logits), logits.stride(0), logits.shape[0], limit, _p(out),
+               stream if stream is not None else current_stream())
+
+
+def sample(logits: torch.Tensor, limit: int, temperature: float, top_k: int, top_p: float, min_p: float,
+           uniform: torch.Tensor, out: torch.Tensor, stream=None) -> None:
+    _need(logits.is_cuda and logits.dtype == torch.float32 and uniform.dtype == torch.float32 and
+          out.dtype == torch.int32, "sample: dtypes")
+    _need(logits.stride(1) == 1 and uniform.numel() >= logits.shape[0] and out.numel() >= logits.shape[0] and
+          0 < limit <= logits.shape[1], "sample: shapes")
+    lib().call("slb_sample", _p(logits), logits.stride(0), logits.shape[0], limit, float(temperature), int(top_k),
+               float(top_p), float(min_p), _p(uniform), _p(out), stream if stream is not None else current_stream())

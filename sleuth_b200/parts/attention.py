@@ -1,0 +1,97 @@
+"""Causal grouped-query attention over the paged cache, as a mixer part.
+
+One fused q/k/v projection (the three matrices are stacked at load time into one
+``[(H + 2K) * head_dim, hidden]`` matrix), then bias, per-head RMSNorm of q and k, rotation and the
+cache write in one kernel, then attention over the cache, then the output projection added into
+the residual stream. Formulas and their order: sleuth/forge/model/attention.py:101-157 (projections
+:106-108, QK-norm before RoPE :121-126, cache update :129-130, scale 1/sqrt(head_dim) :84, GQA
+head mapping :197-199, window mask :160-169, output projection without bias :155-157).
+
+With ``reads_shared_kv`` the part has no k/v projections and reads the cache entry another layer
+application wrote.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.paged import KVRequest
+from ..kernels import ops
+from .base import BuildContext, ParamDecl, Part, build_position, register_mixer
+from .linear import Linear
+from .spec import AttentionSpec
+
+
+class GQAAttention(Part):
+    def __init__(self, spec: AttentionSpec, ctx: BuildContext):
+        if spec.heads % spec.kv_heads:
+            raise ValueError(f"heads ({spec.heads}) must be a multiple of kv_heads ({spec.kv_heads})")
+        if spec.head_dim % 2 or spec.head_dim > 256:
+            raise ValueError(f"head_dim {spec.head_dim} is not supported: it must be even and at most 256")
+        self.spec = spec
+        self.ctx = ctx
+        self.position = build_position(spec.position, ctx)
+        self.scale = spec.scale or 1.0 / math.sqrt(spec.head_dim)
+        self.qkv = self.o = None
+        self.bias = self.q_gain = self.k_gain = None
+
+    # ---- weights ----
+    def declare(self):
+        s = self.spec
+        d = {"q_proj.weight": ParamDecl((s.heads * s.head_dim, s.hidden)),
+             "o_proj.weight": ParamDecl((s.hidden, s.heads * s.head_dim))}
+        if not s.reads_shared_kv:
+            d["k_proj.weight"] = ParamDecl((s.kv_heads * s.head_dim, s.hidden))
+            d["v_proj.weight"] = ParamDecl((s.kv_heads * s.head_dim, s.hidden))
+        if s.qkv_bias:
+            d["q_proj.bias"] = ParamDecl((s.heads * s.head_dim,), "vector")
+            if not s.reads_shared_kv:
+                d["k_proj.bias"] = ParamDecl((s.kv_heads * s.head_dim,), "vector")
+                d["v_proj.bias"] = ParamDecl((s.kv_heads * s.head_dim,), "vector")
+        if s.qk_norm:
+            d["q_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+            if not s.reads_shared_kv:
+                d["k_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+        return d
+
+    def bind(self, t):
+        s = self.spec
+        names = ["q_proj"] if s.reads_shared_kv else ["q_proj", "k_proj", "v_proj"]
+        self.qkv = Linear(torch.cat([t[n + ".weight"] for n in names], dim=0), self.ctx.dtype)
+        self.o = Linear(t["o_proj.weight"], self.ctx.dtype)
+        if s.qkv_bias:
+            self.bias = torch.cat([t[n + ".bias"] for n in names]).contiguous()
+        if s.qk_norm:
+            self.q_gain = t["q_norm.weight"]
+            self.k_gain = t["q_norm.weight"] if s.reads_shared_kv else t["k_norm.weight"]
+
+    def cache_request(self):
+        s = self.spec
+        return KVRequest(s.kv_heads, s.head_dim, s.window)
+
+    # ---- one step ----
+    def forward(self, h, x, b, view, ws):
+        s = self.spec
+        T = h.shape[0]
+        writes = view.writes and not s.reads_shared_kv
+        kvh = 0 if s.reads_shared_kv else s.kv_heads
+        table = b.tables[view.group]
+        mark = ws.mark()
+        qkv = self.qkv.forward(h, ws=ws, stream=b.stream)
+        q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
+        tables = self.position.tables()
+        cos, sin = tables if tables is not None else (None, None)
+        ops.qkv_post(qkv, self.bias, self.q_gain, self.k_gain, cos, sin, q,
+                     view.k_pool if writes else None, view.v_pool if writes else None,
+                     b.tok_seq, b.tok_pos, table, s.heads, kvh, s.head_dim, self.position.rot_dim,
+                     s.qk_norm_eps, b.stream)
+        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
+        ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
+                      s.head_dim, view.window, self.scale, b.stream)
+        self.o.forward(y, into=x, stream=b.stream)
+        ws.release(mark)
+
+
+register_mixer("gqa_attention", GQAAttention)

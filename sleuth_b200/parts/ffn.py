@@ -1,0 +1,41 @@
+"""Feed-forward parts. ``gated_mlp``: down(act(gate(h)) * up(h)) without biases
+(sleuth/forge/model/mlp.py:25-41). Gate and up matrices are stacked at load time into one
+``[2 * intermediate, hidden]`` matrix, so one product feeds the activation kernel."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import BuildContext, ParamDecl, Part, register_ffn
+from .linear import Linear
+from .spec import GatedMLPSpec
+
+
+class GatedMLP(Part):
+    def __init__(self, spec: GatedMLPSpec, ctx: BuildContext):
+        if spec.activation != "silu":
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported (silu)")
+        self.spec, self.ctx = spec, ctx
+        self.gate_up = self.down = None
+
+    def declare(self):
+        s = self.spec
+        return {"gate.weight": ParamDecl((s.intermediate, s.hidden)), "up.weight": ParamDecl((s.intermediate, s.hidden)),
+                "down.weight": ParamDecl((s.hidden, s.intermediate))}
+
+    def bind(self, t):
+        self.gate_up = Linear(torch.cat([t["gate.weight"], t["up.weight"]], dim=0), self.ctx.dtype)
+        self.down = Linear(t["down.weight"], self.ctx.dtype)
+
+    def forward(self, h, x, b, ws):
+        T = h.shape[0]
+        mark = ws.mark()
+        gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
+        act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
+        ops.swiglu(gu, act, b.stream)
+        self.down.forward(act, into=x, stream=b.stream)
+        ws.release(mark)
+
+
+register_ffn("gated_mlp", GatedMLP)

@@ -1,0 +1,47 @@
+"""Arrangements of a mixer, a feed-forward and their norms in one layer.
+
+``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)) (sleuth/forge/model/transformer.py:78,87-88,96,99).
+The layer owns the residual arrangement only; the parts it is given decide everything else. The sum
+itself is a float32 accumulation into the stream, done by the last product of the mixer or ffn.
+"""
+
+from __future__ import annotations
+
+from .base import BuildContext, Part, build_ffn, build_mixer, build_norm, register_layer
+from .spec import LayerSpec
+
+
+class PreNormLayer(Part):
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.ctx = ctx
+        self.norm1 = build_norm(spec.norm1, ctx)
+        self.mixer = build_mixer(spec.mixer, ctx)
+        self.norm2 = build_norm(spec.norm2, ctx)
+        self.ffn = build_ffn(spec.ffn, ctx)
+        self.children = {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn}
+
+    def declare(self):
+        out = {}
+        for prefix, part in self.children.items():
+            for name, decl in part.declare().items():
+                out[f"{prefix}.{name}"] = decl
+        return out
+
+    def bind(self, tensors):
+        for prefix, part in self.children.items():
+            part.bind({k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")})
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, x, b, view, ws):
+        mark = ws.mark()
+        h = ws.take(x.shape, self.ctx.dtype)
+        self.norm1.forward(x, h, stream=b.stream)
+        self.mixer.forward(h, x, b, view, ws)
+        self.norm2.forward(x, h, stream=b.stream)
+        self.ffn.forward(h, x, b, ws)
+        ws.release(mark)
+
+
+register_layer("prenorm", PreNormLayer)

@@ -1,0 +1,86 @@
+"""The matrix product y = h @ W^T that every projection uses, chosen by dtype and row count.
+
+* float32 run: the package's own FMA kernel (``csrc/gemm_f32.cu``); no tensor-core mode, and every
+  output element sums over k in one fixed order whatever the number of rows.
+* bfloat16 run: a library product with float32 accumulation (cuBLAS through ``torch.mm``), as the
+  reference's ``nn.Linear`` (sleuth/forge/model/attention.py:106-108).
+
+``into`` adds the product to a float32 tensor (the residual stream) instead of returning it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+_MODE: dict = {}
+
+
+def _accumulate_mode(device) -> str:
+    """How the bfloat16 library product adds into the float32 stream on this torch build, found once
+    per device by running each form on a 8x8 case: "addmm" (one call, float32 output and addend),
+    "mm32" (float32 output, then the add kernel) or "mm16" (bfloat16 output, then the add kernel)."""
+    key = str(device)
+    if key not in _MODE:
+        a = torch.ones((8, 8), dtype=torch.bfloat16, device=device)
+        c = torch.zeros((8, 8), dtype=torch.float32, device=device)
+        mode = "mm16"
+        try:
+            torch.addmm(c, a, a.t(), out_dtype=torch.float32, out=c)
+            if float(c[0, 0]) == 8.0:
+                mode = "addmm"
+        except (RuntimeError, TypeError):
+            try:
+                torch.mm(a, a.t(), out_dtype=torch.float32, out=c)
+                mode = "mm32"
+            except (RuntimeError, TypeError):
+                pass
+        _MODE[key] = mode
+    return _MODE[key]
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, dtype: torch.dtype):
+        """weight [out, in]: float32 for the 32-bit run, bfloat16 otherwise."""
+        if weight.dtype != dtype:
+            weight = weight.to(dtype)
+        self.weight = weight.contiguous()
+        self.dtype = dtype
+        self.out_features, self.in_features = self.weight.shape
+        self._wt = self.weight.t()      # a view; the library product reads W^T without a copy
+
+    def forward(self, h: torch.Tensor, out: torch.Tensor | None = None, into: torch.Tensor | None = None,
+                ws=None, stream=None, out_dtype: torch.dtype | None = None):
+        M = h.shape[0]
+        if self.dtype == torch.float32:
+            if into is not None:
+                ops.gemm_f32(h, self.weight, into, accumulate=True, stream=stream)
+                return into
+            if out is None:
+                out = ws.take((M, self.out_features), torch.float32)
+            ops.gemm_f32(h, self.weight, out, stream=stream)
+            return out
+        if into is not None:
+            mode = _accumulate_mode(h.device)
+            if mode == "addmm":
+                torch.addmm(into, h, self._wt, out_dtype=torch.float32, out=into)
+            else:
+                mark = ws.mark()
+                tmp = ws.take((M, self.out_features), torch.float32 if mode == "mm32" else self.dtype)
+                if mode == "mm32":
+                    torch.mm(h, self._wt, out_dtype=torch.float32, out=tmp)
+                else:
+                    torch.mm(h, self._wt, out=tmp)
+                ops.add(into, tmp, stream=stream)
+                ws.release(mark)
+            return into
+        want = out_dtype or (out.dtype if out is not None else self.dtype)
+        if out is None:
+            out = ws.take((M, self.out_features), want)
+        if want == self.dtype:
+            torch.mm(h, self._wt, out=out)
+        else:
+            torch.mm(h, self._wt, out_dtype=want, out=out)
+        return out

@@ -1,0 +1,73 @@
+"""Choosing next tokens on the GPU from a logits matrix, for a batch of rows at once.
+
+Pipeline and option meanings are the reference's (sleuth/forge/infer/sampling.py:99-127): ban list,
+repetition penalty, then greedy argmax for temperature <= 0, else temperature, top-k, top-p, min-p
+and a draw. The kernels are in ``csrc/sampling.cu``.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .config import SamplingConfig
+
+
+class Sampler:
+    def __init__(self, device, vocab: int):
+        self.device = torch.device(device)
+        self.vocab = vocab
+        self._out = torch.zeros(1024, dtype=torch.int32, device=self.device)
+        self._host = torch.zeros(1024, dtype=torch.int32).pin_memory()
+
+    def _fit(self, n: int) -> None:
+        if n > self._out.numel():
+            self._out = torch.zeros(2 * n, dtype=torch.int32, device=self.device)
+            self._host = torch.zeros(2 * n, dtype=torch.int32).pin_memory()
+
+    def choose(self, logits: torch.Tensor, cfg: SamplingConfig, uniform: torch.Tensor | np.ndarray | None = None,
+               vocab_limit: int | None = None, recent: list[list[int]] | None = None,
+               banned: list[list[int]] | None = None) -> torch.Tensor:
+        """Tokens for the rows of ``logits`` [n, vocab] as a device int32 tensor [n].
+
+        ``logits`` is changed in place when a ban list or a repetition penalty applies. ``recent``
+        and ``banned`` hold, per row, each token at most once."""
+        n = logits.shape[0]
+        self._fit(n)
+        limit = min(vocab_limit or self.vocab, logits.shape[1])
+        stream = ops.current_stream()
+        rec_t = nrec_t = ban_t = nban_t = None
+        if recent is not None and cfg.repetition_penalty != 1.0 and any(recent):
+            rec_t, nrec_t = self._ragged(recent)
+        if banned is not None and any(banned):
+            # a ban that would forbid every token is ignored (sampling.py:118-120)
+            banned = [b if len({t for t in b if t < limit}) < limit else [] for b in banned]
+            if any(banned):
+                ban_t, nban_t = self._ragged(banned)
+        if rec_t is not None or ban_t is not None:
+            ops.penalize(logits, limit, rec_t, nrec_t, cfg.repetition_penalty, ban_t, nban_t, stream)
+        out = self._out[:n]
+        if cfg.greedy:
+            ops.argmax(logits, limit, out, stream)
+        else:
+            if uniform is None:
+                raise ValueError("sampling with a temperature needs one uniform number per row")
+            if not isinstance(uniform, torch.Tensor):
+                uniform = torch.as_tensor(np.asarray(uniform, dtype=np.float32)).to(self.device)
+            ops.sample(logits, limit, cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p, uniform, out, stream)
+        return out
+
+    def to_host(self, tokens: torch.Tensor) -> list[int]:
+        n = tokens.numel()
+        self._host[:n].copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self._host[:n].tolist()
+
+    def _ragged(self, lists: list[list[int]]):
+        width = max(1, max(len(x) for x in lists))
+        a = np.full((len(lists), width), -1, dtype=np.int32)
+        for i, x in enumerate(lists):
+            a[i, :len(x)] = x
+        counts = np.asarray([len(x) for x in lists], dtype=np.int32)
+        return torch.from_numpy(a).to(self.device), torch.from_numpy(counts).to(self.device)
