@@ -1,0 +1,378 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Qwen3-0.6B-shaped model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 (2,048-token prompts, context
+growing towards 4,096), timed on the device with CUDA events over exactly K decode steps after W
+warm-up steps; a step is one decode step of the whole batch including the choice of the next tokens.
+``e2e`` is the same through the Python entry point (``Engine.generate``: host token lists in, host
+token lists out, one host-to-device copy of the step's tables and one device-to-host read of the
+chosen tokens per step). ``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1
+and 64; ``roofline`` relates the decode step to the memory bandwidth. Weights are random
+(N(0, 0.02)), token ids are seeded uniform: there is no dataset.
+
+``--impl reference`` runs tbertha35/Sleuth itself (installed under baseline/_ref) on the same shapes
+through its own model, cache and sampling code.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG = {  # BASELINE.json configs[2]: Qwen3-0.6B-shaped
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 1024,
+    "intermediate_size": 3072, "num_hidden_layers": 28, "num_attention_heads": 16, "num_key_value_heads": 8,
+    "head_dim": 128, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False,
+    "tie_word_embeddings": True, "max_position_embeddings": 40960,
+}
+PROMPT, CONTEXT, BATCH = 2048, 4096, 8
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ["clocks.sm", "clocks.max.sm", "clocks_event_reasons.hw_slowdown",
+              "clocks_event_reasons.hw_thermal_slowdown", "clocks_event_reasons.sw_thermal_slowdown",
+              "clocks_event_reasons.sw_power_cap"]
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=" + ",".join(self.FIELDS),
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows) -> dict:
+        sm, mx, reasons = [], [], set()
+        for t, cols in self.rows:
+            if len(cols) != len(self.FIELDS) or not any(a <= t <= b for a, b in windows):
+                continue
+            try:
+                sm.append(float(cols[0]))
+                mx.append(float(cols[1]))
+            except ValueError:
+                continue
+            for name, val in zip(self.FIELDS[2:], cols[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name.split(".")[-1])
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def layer_matrix_params(c) -> int:
+    d, hd = c["hidden_size"], c["head_dim"]
+    H, K, I = c["num_attention_heads"], c["num_key_value_heads"], c["intermediate_size"]
+    return d * (H + 2 * K) * hd + H * hd * d + 3 * d * I
+
+
+def prefill_flops(c, T: int) -> float:
+    L, H, hd = c["num_hidden_layers"], c["num_attention_heads"], c["head_dim"]
+    gemm = 2.0 * T * layer_matrix_params(c) * L + 2.0 * c["hidden_size"] * c["vocab_size"]
+    attn = 2.0 * H * hd * T * T * L          # QK^T and PV over the causal half
+    return gemm + attn
+
+
+def kv_bytes_per_token(c, itemsize=2) -> int:
+    return 2 * c["num_key_value_heads"] * c["head_dim"] * itemsize * c["num_hidden_layers"]
+
+
+# ------------------------------------------------------------------------------- ours ----
+
+def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, windows=None):
+    """Prefill ``batch`` prompts of PROMPT tokens, then time ``steps`` decode steps on the device."""
+    import numpy as np
+    import torch
+
+    from sleuth_b200.kernels import ops
+    from sleuth_b200.sampling.config import SamplingConfig
+    rng = np.random.default_rng(seed)
+    V = CONFIG["vocab_size"]
+    prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(batch)]
+    feed = rng.integers(0, V, size=(warmup + steps, batch))
+    greedy = SamplingConfig(temperature=0.0)
+    slots = engine.open(batch)
+    try:
+        logits = engine.prefill(slots, prompts)
+        engine.sampler.choose(logits, greedy)
+        for k in range(warmup):
+            logits = engine.decode(slots, feed[k].tolist())
+            engine.sampler.choose(logits, greedy)
+        torch.cuda.synchronize()
+        lib = ops.lib()
+        own0, g0 = lib.launches, engine.stepper.graph_kernel_launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_a = time.time()
+        start.record()
+        for k in range(warmup, warmup + steps):
+            logits = engine.decode(slots, feed[k].tolist())
+            engine.sampler.choose(logits, greedy)
+        end.record()
+        torch.cuda.synchronize()
+        t_b = time.time()
+        if windows is not None:
+            windows.append((t_a, t_b))
+        ms = start.elapsed_time(end) / steps
+        launches = (lib.launches - own0) + (engine.stepper.graph_kernel_launches - g0)
+        ctx_first = PROMPT + warmup + 1
+        mean_ctx = ctx_first + (steps - 1) / 2.0
+    finally:
+        engine.close(slots)
+    return ms, launches, mean_ctx
+
+
+def prefill_run(engine, warmup: int, iters: int, seed: int, windows=None):
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(seed)
+    prompt = rng.integers(0, CONFIG["vocab_size"], size=PROMPT).tolist()
+    times = []
+    for i in range(warmup + iters):
+        slots = engine.open(1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_a = time.time()
+        a.record()
+        engine.prefill(slots, [prompt])
+        b.record()
+        torch.cuda.synchronize()
+        t_b = time.time()
+        engine.close(slots)
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+            if windows is not None:
+                windows.append((t_a, t_b))
+    return statistics.median(times)
+
+
+def e2e_run(engine, batch: int, steps: int, seed: int, windows=None):
+    """The same decode through ``Engine.generate``: host token lists in and out."""
+    import numpy as np
+
+    from sleuth_b200.sampling.config import SamplingConfig
+    rng = np.random.default_rng(seed)
+    prompts = [rng.integers(0, CONFIG["vocab_size"], size=PROMPT).tolist() for _ in range(batch)]
+    engine.generate(prompts, max_new_tokens=4, sampling=SamplingConfig(temperature=0.0), stop_ids=())   # warm-up
+    t_a = time.time()
+    res = engine.generate(prompts, max_new_tokens=steps + 1, sampling=SamplingConfig(temperature=0.0), stop_ids=())
+    t_b = time.time()
+    if windows is not None:
+        windows.append((t_a, t_b))
+    decoded = sum(len(r.new_ids) - 1 for r in res)
+    seconds = max(r.decode_seconds for r in res)
+    return decoded / seconds, engine.stepper.meta.last_upload_bytes, 4 * batch
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from sleuth_b200.engine.engine import Engine
+    pk = peaks()
+    steps, warmup = args.steps, args.warmup
+    if warmup + steps + 1 > CONTEXT - PROMPT:
+        steps = CONTEXT - PROMPT - warmup - 1
+    layers = args.layers or CONFIG["num_hidden_layers"]
+    cfg = dict(CONFIG, num_hidden_layers=layers)
+    engine = Engine.from_config(cfg, seed=0, dtype="bf16", max_seq_len=CONTEXT, max_tokens=64 * CONTEXT)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+    try:
+        ms, launches, mean_ctx = decode_run(engine, BATCH, steps, warmup, seed=1, windows=windows)
+        value = BATCH * 1000.0 / ms
+        e2e, h2d, d2h = e2e_run(engine, BATCH, steps, seed=1, windows=windows)
+        pre_ms = prefill_run(engine, warmup=3, iters=5, seed=2, windows=windows)
+        ms1, _, _ = decode_run(engine, 1, steps, warmup, seed=3, windows=windows)
+        ms64, _, _ = decode_run(engine, 64, steps, warmup, seed=4, windows=windows)
+    finally:
+        clocks.stop()
+    weight_bytes = engine.model.weight_bytes()
+    step_bytes = weight_bytes + BATCH * mean_ctx * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, PROMPT)
+    pre_tflops = flops / (pre_ms * 1e-3) / 1e12
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, 2,048-token prompts, context to 4,096)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": round(value / 19.0, 1),
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random N(0,0.02) weights)", "impl": "ours",
+        "config": {"model": "Qwen3-0.6B-shaped", "layers": layers, "layers_of_config": CONFIG["num_hidden_layers"],
+                   "hidden": CONFIG["hidden_size"], "heads": CONFIG["num_attention_heads"],
+                   "kv_heads": CONFIG["num_key_value_heads"], "head_dim": CONFIG["head_dim"],
+                   "intermediate": CONFIG["intermediate_size"], "vocab": CONFIG["vocab_size"], "global_batch": BATCH,
+                   "prompt_len": PROMPT, "seq_len": CONTEXT, "mean_context": round(mean_ctx, 1),
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 1.19 GB + cache per step)",
+                   "peaks": pk["source"]},
+        "clocks": clocks.summary(windows),
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches),
+        "prefill": {"value": round(PROMPT / (pre_ms * 1e-3), 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+                    "frac": round(pre_tflops / pk["bf16_tflops"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {"decode_b1": round(1000.0 / ms1, 1), "decode_b64": round(64 * 1000.0 / ms64, 1)},
+    }
+    return out
+
+
+# -------------------------------------------------------------------------- reference ----
+
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "sleuth")):
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no install of the reference (pip --target failed or was not run)"}
+    sys.path.insert(0, ref)
+    try:
+        import numpy as np
+        import torch
+        from sleuth.forge.infer.kv_cache import KVCache
+        from sleuth.forge.infer.sampling import SamplingConfig, sample_next
+        from sleuth.forge.model.config import ModelConfig
+        from sleuth.forge.model.transformer import Transformer
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"the reference does not import here: {type(e).__name__}: {e}"[:300]}
+    c = CONFIG
+    steps, warmup = args.steps, args.warmup
+    if warmup + steps + 1 > CONTEXT - PROMPT:
+        steps = CONTEXT - PROMPT - warmup - 1
+    torch.manual_seed(0)
+    mc = ModelConfig(vocab_size=c["vocab_size"], d_model=c["hidden_size"], n_layers=c["num_hidden_layers"],
+                     n_heads=c["num_attention_heads"], head_size=c["head_dim"], n_kv_heads=c["num_key_value_heads"],
+                     ffn_type="swiglu", ffn_hidden=c["intermediate_size"], norm_eps=c["rms_norm_eps"],
+                     rope_theta=c["rope_theta"], max_seq_len=CONTEXT, qk_norm=True, tie_embeddings=True, pad_vocab_to=1)
+    model = Transformer(mc).to(device="cuda", dtype=torch.bfloat16).eval()
+    rng = np.random.default_rng(1)
+    prompts = torch.tensor(rng.integers(0, c["vocab_size"], size=(BATCH, PROMPT)), device="cuda")
+    feed = rng.integers(0, c["vocab_size"], size=(warmup + steps, BATCH))
+    greedy = SamplingConfig(temperature=0.0)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+    try:
+        with torch.no_grad():
+            def decode(e2e: bool):
+                cache = KVCache.for_model(model, batch=BATCH, max_len=CONTEXT, dtype=torch.bfloat16)
+                logits = model(prompts, cache=cache).logits[:, -1]
+                nxt = sample_next(logits, greedy)
+                for k in range(warmup):
+                    logits = model(torch.tensor(feed[k], device="cuda").view(BATCH, 1), cache=cache).logits[:, -1]
+                    nxt = sample_next(logits, greedy)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t_a = time.time()
+                a.record()
+                host = feed[warmup].tolist()
+                for k in range(warmup, warmup + steps):
+                    ids = torch.tensor(host if e2e else feed[k].tolist(), device="cuda").view(BATCH, 1)
+                    logits = model(ids, cache=cache).logits[:, -1]
+                    nxt = sample_next(logits, greedy)
+                    if e2e:
+                        host = nxt.tolist()
+                b.record()
+                torch.cuda.synchronize()
+                t_b = time.time()
+                windows.append((t_a, t_b))
+                return (a.elapsed_time(b) / steps) if not e2e else (t_b - t_a) * 1000.0 / steps
+
+            ms = decode(False)
+            ms_e2e = decode(True)
+            one = prompts[:1]
+            times = []
+            for i in range(6):
+                cache = KVCache.for_model(model, batch=1, max_len=CONTEXT, dtype=torch.bfloat16)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                model(one, cache=cache).logits[:, -1]
+                b.record()
+                torch.cuda.synchronize()
+                if i:
+                    times.append(a.elapsed_time(b))
+            pre_ms = statistics.median(times)
+    finally:
+        clocks.stop()
+    pk = peaks()
+    value = BATCH * 1000.0 / ms
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, 2,048-token prompts, context to 4,096)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": round(value / 19.0, 1),
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, reference's own random init)",
+        "impl": "reference",
+        "config": {"model": "Qwen3-0.6B-shaped", "layers": c["num_hidden_layers"], "global_batch": BATCH,
+                   "prompt_len": PROMPT, "seq_len": CONTEXT, "parallelism": "single GPU",
+                   "path": "Transformer.forward + KVCache + sample_next, eager (its generate() is batch 1 only)"},
+        "clocks": clocks.summary(windows),
+        "e2e": {"value": round(BATCH * 1000.0 / ms_e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 8 * BATCH,
+                "d2h_bytes_per_step": 8 * BATCH},
+        "gpu_launches": 0,
+        "prefill": {"value": round(PROMPT / (pre_ms * 1e-3), 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+                    "frac": round(prefill_flops(c, PROMPT) / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)},
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2040)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this library runs on a single GPU, --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

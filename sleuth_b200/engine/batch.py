@@ -63,6 +63,7 @@ class MetaStager:
         self.hosts, self.events = [], []
         self.turn = 0
         self.generation = 0
+        self.last_upload_bytes = 0
         self._grow(capacity)
 
     def _grow(self, capacity: int) -> None:
@@ -128,6 +129,7 @@ class MetaStager:
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(st):
             self.dev[:total].copy_(self.hosts[i][:total], non_blocking=True)
+            self.last_upload_bytes = 4 * total
             ev = torch.cuda.Event()
             ev.record(st)
         self.events[i] = ev

@@ -91,6 +91,42 @@ class Engine:
         cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device)
         return cls(cfg, spec, model, cache, device, run_dtype, max_seq_len, unread, use_graphs, max_step_tokens)
 
+    @classmethod
+    def from_config(cls, config_json: dict, seed: int = 0, dtype="bf16", max_seq_len: int = 4096,
+                    max_tokens: int | None = None, device="cuda:0", use_graphs: bool = True,
+                    max_step_tokens: int = 8192, std: float = 0.02) -> "Engine":
+        """A model with random weights drawn on the device from a ``config.json`` dictionary and a
+        seed: matrices and biases ~ N(0, std), norm gains ~ 1 + N(0, std). Nothing is written to disk
+        (``weights.write_random_model`` writes a folder instead, with a generator that is the same on
+        every machine)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("sleuth_b200 runs on an NVIDIA GPU only; torch.cuda.is_available() is False")
+        run_dtype = resolve_dtype(dtype)
+        device = torch.device(device)
+        torch.cuda.set_device(device)
+        arch, cfg, unread = parse_config(config_json)
+        spec = arch.model_spec(cfg)
+        max_seq_len = max(1, min(int(max_seq_len), spec.max_positions))
+        ctx = BuildContext(device=device, dtype=run_dtype, max_positions=-(-max_seq_len // 64) * 64)
+        model = Model(spec, ctx)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(int(seed))
+        tensors = {}
+        for name, d in sorted(model.expected().items()):
+            if d.role == "table":
+                tensors[name] = torch.zeros(d.shape, dtype=torch.int32, device=device)
+                continue
+            t = torch.randn(d.shape, generator=gen, device=device, dtype=torch.float32) * std
+            if d.init == "gain":
+                t += 1.0
+            tensors[name] = t.to(run_dtype) if d.role == "matrix" else t
+        model.bind(tensors)
+        del tensors
+        if max_tokens is None:
+            max_tokens = 8 * max_seq_len
+        cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device)
+        return cls(cfg, spec, model, cache, device, run_dtype, max_seq_len, unread, use_graphs, max_step_tokens)
+
     # ------------------------------------------------------------------ stepping ----
     def open(self, n: int) -> list[int]:
         return self.cache.open(n)

@@ -54,7 +54,8 @@ class Stepper:
         self._seen_decode: set = set()
         self._decode_logits: torch.Tensor | None = None
         self._graph_key = None
-        self.launch_count = 0
+        self._graph_own: dict = {}          # own kernel launches captured in each graph
+        self.graph_kernel_launches = 0      # own kernel launches replayed through graphs so far
         ops.lib()   # build or load the kernels now; fail here, loudly, if that is impossible
 
     # ------------------------------------------------------------------ public ----
@@ -168,11 +169,14 @@ class Stepper:
         graph = self._graphs.get(n)
         if graph is not None:
             graph.replay()
+            self.graph_kernel_launches += self._graph_own[n]
         elif self.use_graphs and n <= self.max_graph_batch and n in self._seen_decode:
+            before = ops.lib().launches
             self._graphs[n] = self._capture(b, logits)
-            key = (self.ws.generation, self.meta.generation)
-            self._graph_key = key
+            self._graph_own[n] = ops.lib().launches - before
+            ops.lib().launches = before          # captured, not run
             self._graphs[n].replay()
+            self.graph_kernel_launches += self._graph_own[n]
         else:
             self.model.forward(b, self.cache, self.ws, logits)
             self._seen_decode.add(n)

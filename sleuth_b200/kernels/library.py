@@ -149,6 +149,7 @@ class KernelLibrary:
         self.dll = ctypes.CDLL(str(path))
         self.dll.slb_last_error.restype = ctypes.c_char_p
         self._fns = {}
+        self.launches = 0      # launcher calls made through ``call`` (each starts at least one kernel)
         for name, argtypes in _SIGNATURES.items():
             self.declare(name, argtypes)
 
@@ -160,6 +161,7 @@ class KernelLibrary:
 
     def call(self, name: str, *args) -> None:
         rc = self._fns[name](*args)
+        self.launches += 1
         if rc != 0:
             raise RuntimeError(self.dll.slb_last_error().decode("utf-8", "replace"))
 
