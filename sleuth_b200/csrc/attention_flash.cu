@@ -1,0 +1,563 @@
+// Causal grouped-query attention over the paged cache on the tensor cores (bfloat16, head sizes 64 and 128).
+//
+// Same contract as the general kernel (attention_generic.cu): a step has written its keys and values to the
+// cache; a query at position p of sequence s sees keys lo..p of s (lo = max(0, p - window + 1) with a window).
+// Formulas: sleuth/forge/model/attention.py:160-206 (mask, 1/sqrt(head_dim) scale, GQA head mapping, float32
+// softmax); the reference itself calls a library kernel here (F.scaled_dot_product_attention, attention.py:171-193).
+//
+// Rows. The G = H / K query heads that share a key/value head are packed into the rows of one tile:
+// row r of (sequence, kv head) is token r / G, head kv * G + r % G. A key/value page (64 keys) loaded once thus
+// serves all G heads, in prefill and in decode alike.
+//
+// Two kernels share the inner loop (S = Q K^T by mma.sync m16n8k16, online softmax in float32 with exp2,
+// O += P V):
+//   * attn_prefill_kernel: a block takes 64 rows of one (sequence, kv head); its 4 warps take 16 rows each
+//     and walk the same key pages, double-buffered through shared memory with cp.async.
+//   * attn_decode_kernel: every sequence brings one token, so a (sequence, kv head) has only G rows. A block
+//     takes one slice of the sequence's pages (split-KV); its 4 warps take 16 keys each of every page, and
+//     their partial results (max, sum, weighted values) are merged through shared memory. With more than one
+//     slice the block writes an unnormalised partial result to scratch memory and attn_combine_kernel merges
+//     the slices.
+// Shared-memory tiles are [64 rows][HD] bfloat16 with the 16-byte chunks of a row XOR-swizzled by the row
+// number, which keeps ldmatrix free of bank conflicts.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace slb {
+
+struct FlashArgs {
+  const __nv_bfloat16* q;       // [tokens, H, HD]
+  const __nv_bfloat16* k_pool;  // [pages, K, 64, HD]
+  const __nv_bfloat16* v_pool;
+  __nv_bfloat16* out;           // [tokens, H * HD]
+  const int* seq_start;         // [n + 1]
+  const int* past;              // [n]
+  const int* counts;            // [n]
+  const int* block_table;       // [n, table_stride]
+  int table_stride;
+  int heads, kv_heads, window;
+  float scale_log2;             // scale * log2(e)
+  // decode only
+  int splits;
+  float* part_o;                // [n, H, splits, HD] unnormalised
+  float* part_ml;               // [n, H, splits, 2]  running max (log2 units) and sum
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of element (row, col) in a swizzled [rows][HD] bf16 tile; col is a multiple of 8
+template <int HD> __device__ __forceinline__ uint32_t swz(int row, int col) {
+  return (uint32_t)(row * (HD * 2) + ((((col >> 3) ^ (row & 7))) << 4));
+}
+
+// Cooperative load of one 64-row page tile (contiguous in global memory) into a swizzled tile.
+template <int HD, int THREADS>
+__device__ __forceinline__ void load_page(uint32_t dst, const __nv_bfloat16* src, int tid) {
+  constexpr int CHUNKS = 64 * HD / 8;
+#pragma unroll
+  for (int i = tid; i < CHUNKS; i += THREADS) {
+    const int row = i / (HD / 8), ch = i % (HD / 8);
+    cp_async16(dst + swz<HD>(row, ch * 8), src + (size_t)row * HD + ch * 8);
+  }
+}
+
+constexpr int kFlashThreads = 128;
+
+// ------------------------------------------------------------------------------------ prefill ----
+template <int HD>
+__global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int TILE = 64 * HD * 2;            // bytes of one [64][HD] tile
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + TILE, sV = sK + 2 * TILE;   // two stages each
+
+  const int seq = blockIdx.z, kh = blockIdx.y;
+  const int G = a.heads / a.kv_heads;
+  const int count = a.counts[seq], past = a.past[seq], tok0 = a.seq_start[seq];
+  const int rows_total = count * G;
+  const int n_tiles = (rows_total + 63) / 64;
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;    // heavy (late) tiles first
+  if (tile >= n_tiles) return;
+  const int r0 = tile * 64;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int t_first = r0 / G;
+  const int t_last = min(rows_total - 1, r0 + 63) / G;
+  const int p_hi = past + t_last;
+  const int key_lo = a.window > 0 ? max(0, past + t_first - a.window + 1) : 0;
+  const int page_lo = key_lo / 64, page_hi = p_hi / 64;
+  const int* table = a.block_table + (size_t)seq * a.table_stride;
+
+  // Q tile: row r <- q[tok0 + r / G, kh * G + r % G, :]
+  for (int i = tid; i < 64 * (HD / 8); i += kFlashThreads) {
+    const int row = i / (HD / 8), ch = i % (HD / 8);
+    const int R = r0 + row;
+    if (R < rows_total) {
+      const __nv_bfloat16* src = a.q + ((size_t)(tok0 + R / G) * a.heads + kh * G + R % G) * HD + ch * 8;
+      cp_async16(sQ + swz<HD>(row, ch * 8), src);
+    } else {
+      *reinterpret_cast<uint4*>(smem + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  {
+    const size_t base = ((size_t)table[page_lo] * a.kv_heads + kh) * 64 * HD;
+    load_page<HD, kFlashThreads>(sK, a.k_pool + base, tid);
+    load_page<HD, kFlashThreads>(sV, a.v_pool + base, tid);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // this warp's 16 query rows as A fragments
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kb = 0; kb < HD / 16; ++kb) {
+    const int row = warp * 16 + (lane & 15), col = kb * 16 + ((lane >> 4) << 3);
+    ldmatrix_x4(qf[kb], sQ + swz<HD>(row, col));
+  }
+  // positions of this thread's two rows (g and g + 8 of the warp's 16)
+  int pos_r[2], lo_r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = r0 + warp * 16 + g + 8 * h;
+    const int p = R < rows_total ? past + R / G : -1;      // -1: a padding row sees nothing
+    pos_r[h] = p;
+    lo_r[h] = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  }
+  const int warp_p_min = past + min(rows_total - 1, r0 + warp * 16) / G;
+  const int warp_R_last = min(rows_total - 1, r0 + warp * 16 + 15);
+  const bool warp_active = r0 + warp * 16 < rows_total;
+  const int warp_lo_max = a.window > 0 ? max(0, past + warp_R_last / G - a.window + 1) : 0;
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+
+  for (int page = page_lo; page <= page_hi; ++page) {
+    const int stage = (page - page_lo) & 1;
+    if (page < page_hi) {
+      const size_t base = ((size_t)table[page + 1] * a.kv_heads + kh) * 64 * HD;
+      load_page<HD, kFlashThreads>(sK + (stage ^ 1) * TILE, a.k_pool + base, tid);
+      load_page<HD, kFlashThreads>(sV + (stage ^ 1) * TILE, a.v_pool + base, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = page * 64;
+    // skip pages that lie wholly after this warp's last row or before its first row's window
+    if (warp_active && key0 <= past + warp_R_last / G && key0 + 63 >= (a.window > 0 ? max(0, warp_p_min - a.window + 1) : 0)) {
+      const uint32_t kS = sK + stage * TILE, vS = sV + stage * TILE;
+      float s[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+      for (int kb = 0; kb < HD / 16; ++kb) {
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {     // 16 keys at a time
+          uint32_t kf[4];
+          const int row = jp * 16 + (lane & 7) + ((lane >> 4) << 3), col = kb * 16 + (((lane >> 3) & 1) << 3);
+          ldmatrix_x4(kf, kS + swz<HD>(row, col));
+          mma_bf16(s[2 * jp], qf[kb], kf[0], kf[1]);
+          mma_bf16(s[2 * jp + 1], qf[kb], kf[2], kf[3]);
+        }
+      }
+      const bool need_mask = key0 + 63 > warp_p_min || key0 < warp_lo_max;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          float v = s[j][e] * a.scale_log2;
+          if (need_mask) {
+            const int key = key0 + j * 8 + 2 * t4 + (e & 1);
+            if (key > pos_r[h] || key < lo_r[h]) v = -INFINITY;
+          }
+          s[j][e] = v;
+          mx[h] = fmaxf(mx[h], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_r[h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
+        alpha[h] = exp2f(m_r[h] - m_use[h]);
+        m_r[h] = m_new;
+      }
+      float sum[2] = {0.0f, 0.0f};
+      uint32_t pf[4][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+        const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+        sum[0] += p0 + p1;
+        sum[1] += p2 + p3;
+        pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_r[h] = l_r[h] * alpha[h] + sum[h];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb) {         // 16 keys at a time
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) { // 16 channels at a time
+          uint32_t vf[4];
+          const int row = kb * 16 + (lane & 15), col = dp * 16 + ((lane >> 4) << 3);
+          ldmatrix_x4_trans(vf, vS + swz<HD>(row, col));
+          mma_bf16(o[2 * dp], pf[kb], vf[0], vf[1]);
+          mma_bf16(o[2 * dp + 1], pf[kb], vf[2], vf[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // the row sums live spread over the 4 threads of a quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 1);
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = r0 + warp * 16 + g + 8 * h;
+    if (R >= rows_total) continue;
+    const float inv = 1.0f / l_r[h];
+    __nv_bfloat16* dst = a.out + ((size_t)(tok0 + R / G) * a.heads + kh * G + R % G) * HD;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const uint32_t v = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------- decode ----
+// grid: (splits * row_tiles, kv_heads, sequences); every sequence has count 1.
+template <int HD>
+__global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int TILE = 64 * HD * 2;
+  const uint32_t sK = smem_u32(smem), sV = sK + 2 * TILE;
+  const uint32_t sQ = sV + 2 * TILE;          // [16][HD]
+  unsigned char* sQ_ptr = smem + 4 * TILE;
+
+  const int seq = blockIdx.z, kh = blockIdx.y;
+  const int G = a.heads / a.kv_heads;
+  const int row_tiles = (G + 15) / 16;
+  const int split = blockIdx.x / row_tiles, rt = blockIdx.x % row_tiles;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int pos = a.past[seq], tok = a.seq_start[seq];
+  const int key_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int page_lo = key_lo / 64, page_hi = pos / 64;
+  const int n_pages = page_hi - page_lo + 1;
+  const int per = (n_pages + a.splits - 1) / a.splits;
+  const int my_lo = page_lo + split * per, my_hi = min(page_hi, my_lo + per - 1);
+  const int* table = a.block_table + (size_t)seq * a.table_stride;
+  const int head0 = kh * G + rt * 16;          // first query head of this row tile
+  const int rows = min(16, G - rt * 16);
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+
+  if (my_lo <= my_hi) {
+    for (int i = tid; i < 16 * (HD / 8); i += kFlashThreads) {
+      const int row = i / (HD / 8), ch = i % (HD / 8);
+      if (row < rows)
+        cp_async16(sQ + swz<HD>(row, ch * 8), a.q + ((size_t)tok * a.heads + head0 + row) * HD + ch * 8);
+      else
+        *reinterpret_cast<uint4*>(sQ_ptr + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
+    }
+    {
+      const size_t base = ((size_t)table[my_lo] * a.kv_heads + kh) * 64 * HD;
+      load_page<HD, kFlashThreads>(sK, a.k_pool + base, tid);
+      load_page<HD, kFlashThreads>(sV, a.v_pool + base, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kb = 0; kb < HD / 16; ++kb) {
+      const int row = lane & 15, col = kb * 16 + ((lane >> 4) << 3);
+      ldmatrix_x4(qf[kb], sQ + swz<HD>(row, col));
+    }
+
+    for (int page = my_lo; page <= my_hi; ++page) {
+      const int stage = (page - my_lo) & 1;
+      if (page < my_hi) {
+        const size_t base = ((size_t)table[page + 1] * a.kv_heads + kh) * 64 * HD;
+        load_page<HD, kFlashThreads>(sK + (stage ^ 1) * TILE, a.k_pool + base, tid);
+        load_page<HD, kFlashThreads>(sV + (stage ^ 1) * TILE, a.v_pool + base, tid);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const int key0 = page * 64 + warp * 16;     // this warp's 16 keys of the page
+      if (key0 <= pos && key0 + 15 >= key_lo) {
+        const uint32_t kS = sK + stage * TILE, vS = sV + stage * TILE;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.0f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+        for (int kb = 0; kb < HD / 16; ++kb) {
+          uint32_t kf[4];
+          const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3), col = kb * 16 + (((lane >> 3) & 1) << 3);
+          ldmatrix_x4(kf, kS + swz<HD>(row, col));
+          mma_bf16(s[0], qf[kb], kf[0], kf[1]);
+          mma_bf16(s[1], qf[kb], kf[2], kf[3]);
+        }
+        float mx = -INFINITY;      // every row of the tile is the same token: one mask for all
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + j * 8 + 2 * t4 + (e & 1);
+            float v = s[j][e] * a.scale_log2;
+            if (key > pos || key < key_lo) v = -INFINITY;
+            s[j][e] = v;
+          }
+        float mxr[2];
+        mxr[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mxr[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        (void)mx;
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mxr[h] = fmaxf(mxr[h], __shfl_xor_sync(0xffffffffu, mxr[h], 1));
+          mxr[h] = fmaxf(mxr[h], __shfl_xor_sync(0xffffffffu, mxr[h], 2));
+          const float m_new = fmaxf(m_r[h], mxr[h]);
+          m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
+          alpha[h] = exp2f(m_r[h] - m_use[h]);
+          m_r[h] = m_new;
+        }
+        uint32_t pf[4];
+        float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+          const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+          sum[0] += p0 + p1;
+          sum[1] += p2 + p3;
+          pf[j * 2 + 0] = pack_bf16(p0, p1);
+          pf[j * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l_r[h] = l_r[h] * alpha[h] + sum[h];
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+          o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+          uint32_t vf[4];
+          const int row = warp * 16 + (lane & 15), col = dp * 16 + ((lane >> 4) << 3);
+          ldmatrix_x4_trans(vf, vS + swz<HD>(row, col));
+          mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+          mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  // merge the four warps (each saw different keys) through shared memory
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 1);
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 2);
+  }
+  float* mo = reinterpret_cast<float*>(smem);            // [4 warps][16 rows][HD]
+  float* mm = mo + 4 * 16 * HD;                          // [4][16]
+  float* ml = mm + 4 * 16;                               // [4][16]
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = g + 8 * h;
+    if (t4 == 0) { mm[warp * 16 + row] = m_r[h]; ml[warp * 16 + row] = l_r[h]; }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      mo[(warp * 16 + row) * HD + i * 8 + 2 * t4] = o[i][2 * h];
+      mo[(warp * 16 + row) * HD + i * 8 + 2 * t4 + 1] = o[i][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * HD; idx += kFlashThreads) {
+    const int row = idx / HD, d = idx % HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mm[w * 16 + row]);
+    const float m_use = m == -INFINITY ? 0.0f : m;
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(mm[w * 16 + row] - m_use);
+      l += ml[w * 16 + row] * f;
+      acc += mo[(w * 16 + row) * HD + d] * f;
+    }
+    const int head = head0 + row;
+    if (a.splits == 1) {
+      a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      const size_t pi = ((size_t)seq * a.heads + head) * a.splits + split;
+      a.part_o[pi * HD + d] = acc;
+      if (d == 0) { a.part_ml[pi * 2] = m; a.part_ml[pi * 2 + 1] = l; }
+    }
+  }
+}
+
+// grid: (sequences * heads); block: HD threads. Merges the slices of attn_decode_kernel.
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_start, int heads,
+                                    int splits, int hd) {
+  const int seq = blockIdx.x / heads, head = blockIdx.x % heads, d = threadIdx.x;
+  const size_t base = ((size_t)seq * heads + head) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  const float m_use = m == -INFINITY ? 0.0f : m;
+  float l = 0.0f, acc = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float f = exp2f(part_ml[(base + s) * 2] - m_use);
+    l += part_ml[(base + s) * 2 + 1] * f;
+    acc += part_o[(base + s) * hd + d] * f;
+  }
+  out[((size_t)seq_start[seq] * heads + head) * hd + d] = __float2bfloat16_rn(acc / l);
+}
+
+template <int HD>
+static int launch_prefill(const FlashArgs& a, int n_seqs, int max_count, cudaStream_t s) {
+  const int G = a.heads / a.kv_heads;
+  const int tiles = (max_count * G + 63) / 64;
+  const int smem = 5 * 64 * HD * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(2, "attention (prefill): cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(tiles, a.kv_heads, n_seqs);
+  attn_prefill_kernel<HD><<<grid, kFlashThreads, smem, s>>>(a);
+  return check_launch("attention (prefill)");
+}
+
+template <int HD>
+static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
+  const int G = a.heads / a.kv_heads;
+  const int row_tiles = (G + 15) / 16;
+  const int tiles_bytes = 4 * 64 * HD * 2 + 16 * HD * 2;
+  const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * 4;
+  const int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(2, "attention (decode): cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(a.splits * row_tiles, a.kv_heads, n_seqs);
+  attn_decode_kernel<HD><<<grid, kFlashThreads, smem, s>>>(a);
+  int rc = check_launch("attention (decode)");
+  if (rc || a.splits == 1) return rc;
+  attn_combine_kernel<<<n_seqs * a.heads, HD, 0, s>>>(a.part_o, a.part_ml, a.out, a.seq_start, a.heads, a.splits, HD);
+  return check_launch("attention (combine)");
+}
+
+}  // namespace slb
+
+using namespace slb;
+
+// 1 when the tensor-core kernels take this shape, else 0 (the general kernel then serves it).
+extern "C" int slb_attention_flash_supported(int head_dim, int dtype) {
+  return dtype == kBF16 && (head_dim == 64 || head_dim == 128);
+}
+
+// Scratch floats a decode call with `splits` slices needs: partial values plus (max, sum) pairs.
+extern "C" long long slb_attention_decode_scratch_floats(int n_seqs, int heads, int head_dim, int splits) {
+  return splits <= 1 ? 0 : (long long)n_seqs * heads * splits * (head_dim + 2);
+}
+
+extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                     const int* seq_start, const int* past, const int* counts, const int* block_table,
+                                     int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
+                                     int window, float scale, void* stream) {
+  SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+              "attention (prefill): seqs=%d max_count=%d heads=%d kv_heads=%d", n_seqs, max_count, heads, kv_heads);
+  SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (prefill): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
+  SLB_REQUIRE(window >= 0 && table_stride > 0 && n_seqs < 65536 && kv_heads < 65536, "attention (prefill): window=%d table_stride=%d", window, table_stride);
+  if (n_seqs == 0 || max_count == 0) return 0;
+  FlashArgs a{};
+  a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+  a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts;
+  a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;
+  a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = 1;
+  return head_dim == 64 ? launch_prefill<64>(a, n_seqs, max_count, (cudaStream_t)stream)
+                        : launch_prefill<128>(a, n_seqs, max_count, (cudaStream_t)stream);
+}
+
+extern "C" int slb_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                    const int* seq_start, const int* past, const int* block_table, int table_stride,
+                                    int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
+                                    int splits, float* scratch, long long scratch_floats, void* stream) {
+  SLB_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+              "attention (decode): seqs=%d heads=%d kv_heads=%d", n_seqs, heads, kv_heads);
+  SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (decode): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
+  SLB_REQUIRE(window >= 0 && table_stride > 0 && splits >= 1 && n_seqs < 65536 && kv_heads < 65536,
+              "attention (decode): window=%d table_stride=%d splits=%d", window, table_stride, splits);
+  const long long need = slb_attention_decode_scratch_floats(n_seqs, heads, head_dim, splits);
+  SLB_REQUIRE(need == 0 || (scratch != nullptr && scratch_floats >= need),
+              "attention (decode): %d slices need %lld floats of scratch memory, %lld were given", splits, need, scratch_floats);
+  if (n_seqs == 0) return 0;
+  FlashArgs a{};
+  a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+  a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = nullptr;
+  a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;
+  a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = splits;
+  a.part_o = scratch;
+  a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
+  return head_dim == 64 ? launch_decode<64>(a, n_seqs, (cudaStream_t)stream)
+                        : launch_decode<128>(a, n_seqs, (cudaStream_t)stream);
+}

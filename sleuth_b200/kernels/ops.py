@@ -117,6 +117,52 @@ def attention(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, heads: int,
                DT[q.dtype], stream if stream is not None else current_stream())
 
 
+def flash_supported(head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core attention kernels take this head size and dtype."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128)
+
+
+def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> int:
+    """Slices of the key range per (sequence, kv head) in a decode step: enough blocks to fill the
+    GPU a few times over, never more than a sequence can have pages. It depends on the batch size
+    only, not on the lengths, so a captured step stays valid as sequences grow."""
+    blocks = max(1, n_seqs * kv_heads * ((group + 15) // 16))
+    return max(1, min(-(-592 // blocks), 32, table_stride))
+
+
+def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
+                      kv_heads: int, head_dim: int, window: int, scale: float, stream=None) -> None:
+    """Tensor-core attention for a step in which sequences bring any number of tokens."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    T, n = q.shape[0], block_table.shape[0]
+    _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
+    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
+    _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
+    lib().call("slb_attention_prefill", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
+               _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
+               float(scale), stream if stream is not None else current_stream())
+
+
+def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
+                     window: int, scale: float, splits: int, scratch, stream=None) -> None:
+    """Tensor-core attention for a step in which every sequence brings one token (split-KV)."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch)
+    n = block_table.shape[0]
+    _need(q.shape == (n, heads, head_dim) and out.shape == (n, heads * head_dim), "attention: shapes disagree")
+    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
+    _need(scratch is None or scratch.dtype == torch.float32, "attention: scratch is float32")
+    lib().call("slb_attention_decode", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
+               _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
+               int(splits), _p(scratch), 0 if scratch is None else scratch.numel(),
+               stream if stream is not None else current_stream())
+
+
+def decode_scratch_floats(n_seqs: int, heads: int, head_dim: int, splits: int) -> int:
+    return 0 if splits <= 1 else n_seqs * heads * splits * (head_dim + 2)
+
+
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, accumulate: bool = False,
              stream=None) -> None:
     """out[M, N] (+)= a[M, K] @ w[N, K]^T (+ bias), all float32, plain FMA."""

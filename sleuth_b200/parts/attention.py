@@ -88,8 +88,18 @@ class GQAAttention(Part):
                      b.tok_seq, b.tok_pos, table, s.heads, kvh, s.head_dim, self.position.rot_dim,
                      s.qk_norm_eps, b.stream)
         y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
-        ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
-                      s.head_dim, view.window, self.scale, b.stream)
+        if not ops.flash_supported(s.head_dim, self.ctx.dtype):
+            ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
+                          s.head_dim, view.window, self.scale, b.stream)
+        elif b.max_count == 1:
+            splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
+            floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
+            scratch = ws.take((floats,), torch.float32) if floats else None
+            ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
+                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream)
+        else:
+            ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
+                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
         self.o.forward(y, into=x, stream=b.stream)
         ws.release(mark)
 

@@ -1,0 +1,266 @@
+"""Each CUDA kernel alone against a plain float64 computation of the same formula, at sizes other than
+the engine's: odd widths, head sizes 16..256, groups of 1..8 heads, windows, pages in scrambled order."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from sleuth_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------ row-wise kernels ----
+
+@pytest.mark.parametrize("dim", [64, 96, 1000, 1024, 2050])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(dim, dtype):
+    g = torch.Generator().manual_seed(dim)
+    x = torch.randn(7, dim, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(dim, generator=g)
+    eps = 1e-5
+    ref = (x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * w.double())
+    out = torch.empty(7, dim, dtype=dtype, device=DEV)
+    ops().rmsnorm(x.to(DEV), w.to(DEV), out, eps)
+    torch.testing.assert_close(out.cpu().double(), ref, **tol(dtype))
+    # chosen rows only
+    rows = torch.tensor([5, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, dim, dtype=dtype, device=DEV)
+    ops().rmsnorm(x.to(DEV), w.to(DEV), out2, eps, rows)
+    torch.testing.assert_close(out2.cpu().double(), ref[[5, 0, 3]], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_add_swiglu(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(37, 50, generator=g).to(dtype)
+    ids = torch.tensor([3, 36, 0, 3, 17], dtype=torch.int32)
+    x = torch.empty(5, 50, dtype=torch.float32, device=DEV)
+    ops().embed(ids.to(DEV), table.to(DEV), x, 1.5)
+    torch.testing.assert_close(x.cpu(), table[ids.long()].float() * 1.5)
+    delta = torch.randn(5, 50, generator=g).to(dtype)
+    ops().add(x, delta.to(DEV))
+    torch.testing.assert_close(x.cpu(), table[ids.long()].float() * 1.5 + delta.float())
+    gu = torch.randn(6, 2 * 77, generator=g).to(dtype)
+    act = torch.empty(6, 77, dtype=dtype, device=DEV)
+    ops().swiglu(gu.to(DEV), act)
+    gd, ud = gu[:, :77].double(), gu[:, 77:].double()
+    torch.testing.assert_close(act.cpu().double(), gd * torch.sigmoid(gd) * ud, **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 33, 17), (5, 64, 96), (16, 503, 160), (17, 100, 1000), (130, 257, 75)])
+def test_gemm_f32_exact_and_row_independent(M, N, K):
+    g = torch.Generator().manual_seed(M * N)
+    a, w, bias = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a.to(DEV), w.to(DEV), out, bias.to(DEV))
+    ref = a.double() @ w.double().T + bias.double()
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=1e-5, atol=1e-4)
+    # a row computed alone equals the same row computed in the batch, bit for bit
+    one = torch.empty(1, N, device=DEV)
+    ops().gemm_f32(a[M - 1:M].contiguous().to(DEV), w.to(DEV), one, bias.to(DEV))
+    assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
+    # accumulate adds to what is there
+    acc = torch.full((M, N), 2.0, device=DEV)
+    ops().gemm_f32(a.to(DEV), w.to(DEV), acc, None, accumulate=True)
+    torch.testing.assert_close(acc.cpu().double(), a.double() @ w.double().T + 2.0, rtol=1e-5, atol=1e-4)
+
+
+# ------------------------------------------------------------------ cache layout helpers ----
+
+def make_cache(seq_lens, kv_heads, hd, dtype, gen, scramble=True):
+    """Random keys/values for sequences of the given lengths, laid out in pages in scrambled order.
+    Returns (k_pool, v_pool, table [n, stride], dense keys, dense values) with dense [n][len, K, hd]."""
+    n = len(seq_lens)
+    stride = max(1, max((l + 63) // 64 for l in seq_lens))
+    total = sum((l + 63) // 64 for l in seq_lens) + 3
+    order = torch.randperm(total, generator=gen).tolist() if scramble else list(range(total))
+    k_pool = torch.full((total, kv_heads, 64, hd), float("nan")).to(dtype)
+    v_pool = torch.full((total, kv_heads, 64, hd), float("nan")).to(dtype)
+    table = torch.full((n, stride), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for i, l in enumerate(seq_lens):
+        k = torch.randn(l, kv_heads, hd, generator=gen).to(dtype)
+        v = torch.randn(l, kv_heads, hd, generator=gen).to(dtype)
+        ks.append(k)
+        vs.append(v)
+        for pg in range((l + 63) // 64):
+            page = order.pop()
+            table[i, pg] = page
+            a, b = pg * 64, min(l, pg * 64 + 64)
+            k_pool[page, :, :b - a] = k[a:b].transpose(0, 1)
+            v_pool[page, :, :b - a] = v[a:b].transpose(0, 1)
+    return k_pool, v_pool, table, ks, vs
+
+
+def plain_attention(q, k, v, pos, window, scale):
+    """q [T, H, hd] at positions pos[t]; k, v [L, K, hd] of the same sequence; float64."""
+    T, H, hd = q.shape
+    K = k.shape[1]
+    out = torch.zeros(T, H, hd, dtype=torch.float64)
+    for t in range(T):
+        lo = max(0, pos[t] - window + 1) if window else 0
+        for h in range(H):
+            kk = k[lo:pos[t] + 1, h // (H // K)].double()
+            vv = v[lo:pos[t] + 1, h // (H // K)].double()
+            s = (kk @ q[t, h].double()) * scale
+            out[t, h] = torch.softmax(s, 0) @ vv
+    return out
+
+
+def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed):
+    o = ops()
+    gen = torch.Generator().manual_seed(seed)
+    lens = [p + c for p, c in zip(pasts, counts)]
+    k_pool, v_pool, table, ks, vs = make_cache(lens, kv_heads, hd, dtype, gen)
+    T = sum(counts)
+    q = torch.randn(T, heads, hd, generator=gen).to(dtype)
+    # make one far key decisive for some query: scale a key and the matching query channel up
+    scale = 1.0 / math.sqrt(hd)
+    tok_seq = np.repeat(np.arange(len(counts)), counts).astype(np.int32)
+    starts = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(p, p + c) for p, c in zip(pasts, counts)]).astype(np.int32)
+    ref = torch.cat([plain_attention(q[starts[i]:starts[i + 1]].float(), ks[i].float(), vs[i].float(),
+                                     tok_pos[starts[i]:starts[i + 1]], window, scale) for i in range(len(counts))])
+    d = lambda a: torch.as_tensor(a).to(DEV)
+    out = torch.full((T, heads * hd), float("nan")).to(dtype).to(DEV)
+    if kind == "generic":
+        o.attention(d(q), d(k_pool), d(v_pool), out, d(tok_seq), d(tok_pos), d(table), heads, kv_heads, hd, window, scale)
+    elif kind == "prefill":
+        o.attention_prefill(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)),
+                            d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale)
+    else:
+        splits = kind
+        floats = o.decode_scratch_floats(len(counts), heads, hd, splits)
+        scratch = torch.full((max(floats, 1),), float("nan"), device=DEV)
+        o.attention_decode(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)), d(table),
+                           heads, kv_heads, hd, window, scale, splits, scratch if floats else None)
+    got = out.cpu().double().view(T, heads, hd)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, ref, **(dict(rtol=2e-2, atol=1.5e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 16), (6, 3, 24), (5, 1, 64), (8, 8, 40), (2, 1, 256), (16, 2, 128)])
+def test_attention_generic(dtype, heads, kv_heads, hd):
+    run_attention("generic", dtype, heads, kv_heads, hd, pasts=[0, 70, 0, 129], counts=[5, 1, 67, 3], window=0, seed=hd)
+    run_attention("generic", dtype, heads, kv_heads, hd, pasts=[0, 100], counts=[90, 2], window=33, seed=hd + 1)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 128), (5, 1, 64), (8, 8, 64), (16, 2, 128), (6, 2, 128), (32, 1, 64)])
+def test_attention_prefill_tensor_cores(heads, kv_heads, hd):
+    bf = torch.bfloat16
+    run_attention("prefill", bf, heads, kv_heads, hd, pasts=[0, 0, 0], counts=[1, 64, 200], window=0, seed=1)
+    run_attention("prefill", bf, heads, kv_heads, hd, pasts=[70, 0, 129, 5], counts=[33, 5, 1, 130], window=0, seed=2)
+    run_attention("prefill", bf, heads, kv_heads, hd, pasts=[0, 150], counts=[170, 40], window=50, seed=3)
+    run_attention("prefill", bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 128), (5, 1, 64), (8, 8, 64), (16, 2, 128), (40, 2, 64)])
+def test_attention_decode_tensor_cores(splits, heads, kv_heads, hd):
+    bf = torch.bfloat16
+    run_attention(splits, bf, heads, kv_heads, hd, pasts=[0, 63, 64, 300, 1000], counts=[1] * 5, window=0, seed=5)
+    run_attention(splits, bf, heads, kv_heads, hd, pasts=[10, 200, 700], counts=[1] * 3, window=100, seed=6)
+
+
+def test_attention_far_key_decides():
+    """One key far back gets a score that dominates: a kernel that drops or misplaces it fails loudly."""
+    o = ops()
+    for dtype, kind in ((torch.float32, "generic"), (torch.bfloat16, "decode"), (torch.bfloat16, "prefill")):
+        gen = torch.Generator().manual_seed(9)
+        H, K, hd, L = 4, 2, 128, 700
+        k_pool, v_pool, table, ks, vs = make_cache([L], K, hd, dtype, gen)
+        far = 37
+        page, row = int(table[0, far // 64]), far % 64
+        q = torch.randn(1, H, hd, generator=gen).to(dtype)
+        k_pool[page, :, row] = (q[0, ::2] * 4).to(dtype)            # key 37 of each kv head lines up with its first query head
+        v_pool[page, :, row] = 7.0
+        d = lambda a: torch.as_tensor(a).to(DEV)
+        out = torch.empty(1, H * hd, dtype=dtype, device=DEV)
+        i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        if kind == "generic":
+            o.attention(d(q), d(k_pool), d(v_pool), out, i32(0), i32(L - 1), d(table), H, K, hd, 0, 1.0)
+        elif kind == "decode":
+            scratch = torch.empty(o.decode_scratch_floats(1, H, hd, 4), device=DEV)
+            o.attention_decode(d(q), d(k_pool), d(v_pool), out, i32(0, 1), i32(L - 1), d(table), H, K, hd, 0, 1.0, 4, scratch)
+        else:
+            # two tokens so that the prefill kernel is the one that fits; look at the last one
+            q2 = torch.cat([q, q]).contiguous()
+            out2 = torch.empty(2, H * hd, dtype=dtype, device=DEV)
+            o.attention_prefill(d(q2), d(k_pool), d(v_pool), out2, i32(0, 2), i32(L - 2), i32(2), d(table), 2, H, K, hd, 0, 1.0)
+            out = out2[1:]
+        got = out.cpu().float().view(H, hd)
+        assert (got[0] - 7.0).abs().max() < 0.05 and (got[2] - 7.0).abs().max() < 0.05
+
+
+# ------------------------------------------------------------------ qkv_post ----
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,hd,rot", [(4, 2, 16, 16), (6, 3, 24, 24), (5, 1, 64, 32), (2, 2, 128, 128), (3, 1, 256, 0)])
+def test_qkv_post(dtype, heads, kv_heads, hd, rot):
+    o = ops()
+    gen = torch.Generator().manual_seed(hd + heads)
+    pasts, counts = [0, 100, 63], [3, 2, 70]
+    lens = [p + c for p, c in zip(pasts, counts)]
+    T = sum(counts)
+    rows = heads + 2 * kv_heads
+    qkv = torch.randn(T, rows * hd, generator=gen).to(dtype)
+    bias = torch.randn(rows * hd, generator=gen) * 0.1
+    qg, kg = 1 + 0.1 * torch.randn(hd, generator=gen), 1 + 0.1 * torch.randn(hd, generator=gen)
+    eps, theta, maxpos = 1e-5, 1e4, 256
+    cos = sin = None
+    if rot:
+        inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        ang = torch.outer(torch.arange(maxpos, dtype=torch.float32), inv)
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    stride = max((l + 63) // 64 for l in lens)
+    n_pages = sum((l + 63) // 64 for l in lens)
+    perm = torch.randperm(n_pages, generator=gen).tolist()
+    table = torch.full((len(lens), stride), -1, dtype=torch.int32)
+    for i, l in enumerate(lens):
+        for pg in range((l + 63) // 64):
+            table[i, pg] = perm.pop()
+    tok_seq = np.repeat(np.arange(3), counts).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(p, p + c) for p, c in zip(pasts, counts)]).astype(np.int32)
+    d = lambda a: None if a is None else torch.as_tensor(a).to(DEV)
+    q_out = torch.empty(T, heads, hd, dtype=dtype, device=DEV)
+    k_pool = torch.zeros(n_pages, kv_heads, 64, hd, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    o.qkv_post(d(qkv), d(bias), d(qg), d(kg), d(cos), d(sin), q_out, k_pool, v_pool, d(tok_seq), d(tok_pos), d(table),
+               heads, kv_heads, hd, rot, eps)
+    x = qkv.double().view(T, rows, hd) + bias.double().view(rows, hd)
+
+    def norm(v, gain):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * gain.double()
+
+    def rope(v):
+        if not rot:
+            return v
+        c, s = cos[tok_pos].double()[:, None, :], sin[tok_pos].double()[:, None, :]
+        a, b = v[..., :rot // 2], v[..., rot // 2:rot]
+        return torch.cat([a * c - b * s, b * c + a * s, v[..., rot:]], dim=-1)
+
+    q_ref = rope(norm(x[:, :heads], qg))
+    k_ref = rope(norm(x[:, heads:heads + kv_heads], kg))
+    v_ref = x[:, heads + kv_heads:]
+    tl = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(q_out.cpu().double(), q_ref, **tl)
+    kp, vp = k_pool.cpu().double(), v_pool.cpu().double()
+    for t in range(T):
+        page = int(table[tok_seq[t], tok_pos[t] // 64])
+        torch.testing.assert_close(kp[page, :, tok_pos[t] % 64], k_ref[t], **tl)
+        torch.testing.assert_close(vp[page, :, tok_pos[t] % 64], v_ref[t], **tl)

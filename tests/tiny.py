@@ -1,0 +1,31 @@
+"""The tiny Qwen3 configurations of the tests. They differ in every size and option: layers, width,
+query and key/value heads (and so the group size), head size (16, 24 with heads * head_dim != width,
+64 for the tensor-core kernels, 32), intermediate size, vocabulary (no power of two in B and C),
+rope_theta, rms_norm_eps, q/k/v biases, tied or separate output matrix, context, and a sliding
+window on some layers (C)."""
+
+A = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256, hidden_size=64,
+         intermediate_size=192, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+         rope_theta=10000.0, rms_norm_eps=1e-6, attention_bias=False, tie_word_embeddings=True,
+         max_position_embeddings=128)
+
+B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=503, hidden_size=96,
+         intermediate_size=160, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=3, head_dim=24,
+         rope_theta=1000000.0, rms_norm_eps=1e-5, attention_bias=True, tie_word_embeddings=False,
+         max_position_embeddings=256)
+
+# head_dim 64 takes the tensor-core attention kernels in bfloat16; one KV head (group of 5); windows on two layers
+C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=311, hidden_size=80,
+         intermediate_size=136, num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=1, head_dim=64,
+         rope_theta=50000.0, rms_norm_eps=3e-6, attention_bias=True, tie_word_embeddings=True,
+         max_position_embeddings=512, sliding_window=40,
+         layer_types=["full_attention", "sliding_attention", "full_attention", "sliding_attention"])
+
+# head_dim 128, the benchmark's head size, with a group of 2; long context for the long-decoding test
+D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=640, hidden_size=128,
+         intermediate_size=200, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+         rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False, tie_word_embeddings=False,
+         max_position_embeddings=1024)
+
+CONFIGS = {"A": A, "B": B, "C": C, "D": D}
+SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44}
