@@ -77,14 +77,21 @@ template <int HD> __device__ __forceinline__ uint32_t swz(int row, int col) {
   return (uint32_t)(row * (HD * 2) + ((((col >> 3) ^ (row & 7))) << 4));
 }
 
-// Cooperative load of one 64-row page tile (contiguous in global memory) into a swizzled tile.
+// Cooperative load of one 64-row page tile (contiguous in global memory) into a swizzled tile. Rows from
+// `valid_rows` on lie beyond the sequence's length: a reused page holds another sequence's leftovers there, and
+// although their weights are exactly zero, 0 * inf would still poison the sum, so they are filled with zeros.
 template <int HD, int THREADS>
-__device__ __forceinline__ void load_page(uint32_t dst, const __nv_bfloat16* src, int tid) {
+__device__ __forceinline__ void load_page(unsigned char* smem_base, uint32_t dst_off, const __nv_bfloat16* src,
+                                          int valid_rows, int tid) {
   constexpr int CHUNKS = 64 * HD / 8;
+  const uint32_t dst = smem_u32(smem_base) + dst_off;
 #pragma unroll
   for (int i = tid; i < CHUNKS; i += THREADS) {
     const int row = i / (HD / 8), ch = i % (HD / 8);
-    cp_async16(dst + swz<HD>(row, ch * 8), src + (size_t)row * HD + ch * 8);
+    if (row < valid_rows)
+      cp_async16(dst + swz<HD>(row, ch * 8), src + (size_t)row * HD + ch * 8);
+    else
+      *reinterpret_cast<uint4*>(smem_base + dst_off + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -127,10 +134,11 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
       *reinterpret_cast<uint4*>(smem + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
     }
   }
+  const int seq_len = past + count;
   {
     const size_t base = ((size_t)table[page_lo] * a.kv_heads + kh) * 64 * HD;
-    load_page<HD, kFlashThreads>(sK, a.k_pool + base, tid);
-    load_page<HD, kFlashThreads>(sV, a.v_pool + base, tid);
+    load_page<HD, kFlashThreads>(smem, TILE, a.k_pool + base, seq_len - page_lo * 64, tid);
+    load_page<HD, kFlashThreads>(smem, 3 * TILE, a.v_pool + base, seq_len - page_lo * 64, tid);
   }
   cp_async_commit();
   cp_async_wait<0>();
@@ -166,8 +174,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
     const int stage = (page - page_lo) & 1;
     if (page < page_hi) {
       const size_t base = ((size_t)table[page + 1] * a.kv_heads + kh) * 64 * HD;
-      load_page<HD, kFlashThreads>(sK + (stage ^ 1) * TILE, a.k_pool + base, tid);
-      load_page<HD, kFlashThreads>(sV + (stage ^ 1) * TILE, a.v_pool + base, tid);
+      load_page<HD, kFlashThreads>(smem, (1 + (stage ^ 1)) * TILE, a.k_pool + base, seq_len - (page + 1) * 64, tid);
+      load_page<HD, kFlashThreads>(smem, (3 + (stage ^ 1)) * TILE, a.v_pool + base, seq_len - (page + 1) * 64, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -312,8 +320,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     }
     {
       const size_t base = ((size_t)table[my_lo] * a.kv_heads + kh) * 64 * HD;
-      load_page<HD, kFlashThreads>(sK, a.k_pool + base, tid);
-      load_page<HD, kFlashThreads>(sV, a.v_pool + base, tid);
+      load_page<HD, kFlashThreads>(smem, 0, a.k_pool + base, pos + 1 - my_lo * 64, tid);
+      load_page<HD, kFlashThreads>(smem, 2 * TILE, a.v_pool + base, pos + 1 - my_lo * 64, tid);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -329,8 +337,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       const int stage = (page - my_lo) & 1;
       if (page < my_hi) {
         const size_t base = ((size_t)table[page + 1] * a.kv_heads + kh) * 64 * HD;
-        load_page<HD, kFlashThreads>(sK + (stage ^ 1) * TILE, a.k_pool + base, tid);
-        load_page<HD, kFlashThreads>(sV + (stage ^ 1) * TILE, a.v_pool + base, tid);
+        load_page<HD, kFlashThreads>(smem, (stage ^ 1) * TILE, a.k_pool + base, pos + 1 - (page + 1) * 64, tid);
+        load_page<HD, kFlashThreads>(smem, (2 + (stage ^ 1)) * TILE, a.v_pool + base, pos + 1 - (page + 1) * 64, tid);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
