@@ -72,9 +72,11 @@ class Qwen3Config:
                  f"layer_types has {len(self.layer_types)} entries for {self.num_hidden_layers} layers")
             bad = sorted(set(self.layer_types) - {"full_attention", "sliding_attention"})
             need(not bad, f"layer_types entries must be 'full_attention' or 'sliding_attention', got {bad}")
-        if any(self.windows):
+        if self.layer_types is not None and "sliding_attention" in self.layer_types:
             need(self.sliding_window is not None and self.sliding_window > 0,
-                 "sliding-window layers need sliding_window > 0")
+                 "layer_types names sliding_attention layers, which need sliding_window > 0")
+        if self.sliding_window is not None:
+            need(self.sliding_window > 0, f"sliding_window must be positive, got {self.sliding_window}")
 
     # ---- derived ----
     @property

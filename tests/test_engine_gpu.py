@@ -1,0 +1,268 @@
+"""The engine against the plain implementation, in float32 and in bfloat16, under every schedule:
+each request alone and whole; its last 32 tokens one by one; batches of unequal lengths whose shorter
+requests end earlier, batch after batch so that slots and pages are used again; long decoding; the
+first tokens of a sequence; greedy generation through the entry point; sampling."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import tiny
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+# Decided before the first run. float32: the engine and the plain code differ by summation order only.
+# bfloat16: weights are compared rounded alike, activations and cache entries are rounded in the engine
+# only; logits of these tiny models are of order 1.
+TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=4e-2, atol=4e-2)}
+
+
+def load(folder, dtype, max_tokens=4096, **kw):
+    import sleuth_b200 as sb
+    cfg = plain.read_model(folder)[0]
+    return sb.load(folder, dtype=dtype, max_seq_len=cfg["max_position_embeddings"], max_tokens=max_tokens, **kw)
+
+
+def oracle(folder, dtype):
+    cfg, w = plain.read_model(folder)
+    cache = {}
+
+    def f(ids):
+        key = tuple(ids)
+        if key not in cache:
+            cache[key] = plain.logits(cfg, w, list(ids), round_weights_to_bf16=(dtype == "bf16"))
+        return cache[key]
+    return f
+
+
+def requests_for(name, lengths, seed=0):
+    rng = np.random.default_rng(seed + tiny.SEEDS[name])
+    return [rng.integers(0, tiny.CONFIGS[name]["vocab_size"], size=n).tolist() for n in lengths]
+
+
+LENGTHS = {"A": [5, 11, 17, 70], "B": [1, 7, 23, 40, 130], "C": [3, 64, 65, 150, 33], "D": [40, 1, 200, 129]}
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_each_request_alone_and_whole(name, dtype, model_folders):
+    eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
+    for ids in requests_for(name, LENGTHS[name]):
+        (slot,) = eng.open(1)
+        got = eng.step([(slot, ids, tuple(range(len(ids))))]).cpu()
+        eng.close([slot])
+        torch.testing.assert_close(got, ref(ids), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_last_32_tokens_one_by_one(name, dtype, model_folders):
+    eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
+    for ids in requests_for(name, [n for n in LENGTHS[name] if n > 32] + [33]):
+        cut = len(ids) - 32
+        (slot,) = eng.open(1)
+        rows = [eng.step([(slot, ids[:cut], (cut - 1,))]).cpu()]
+        for t in ids[cut:]:
+            rows.append(eng.step([(slot, [t], (0,))]).cpu().clone())
+        eng.close([slot])
+        torch.testing.assert_close(torch.cat(rows), ref(ids)[cut - 1:], **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_unequal_batches_one_after_another_reuse_slots(name, dtype, model_folders):
+    """Three batches through a cache with room for one batch only. Within a batch the requests have unequal
+    prompts and unequal numbers of decoded tokens, so the shorter ones end earlier; the next batch gets
+    the same slots and pages, still full of the previous batch's keys."""
+    max_tokens = 64 * 8
+    eng, ref = load(model_folders[name], dtype, max_tokens=max_tokens), oracle(model_folders[name], dtype)
+    ctx = tiny.CONFIGS[name]["max_position_embeddings"]
+    plans = [[(100, 20), (60, 3), (5, 27)], [(1, 12), (64, 1), (63, 2), (30, 30)], [(90, 9), (2, 40)]]
+    used_slots = []
+    for b, plan in enumerate(plans):
+        plan = [(p, d) for p, d in plan if p + d <= ctx]
+        reqs = requests_for(name, [p + d for p, d in plan], seed=b)
+        slots = eng.open(len(reqs))
+        used_slots.append(set(slots))
+        got = {i: [] for i in range(len(reqs))}
+        out = eng.step([(s, ids[:p], (p - 1,)) for s, ids, (p, d) in zip(slots, reqs, plan)]).cpu()
+        for i in range(len(reqs)):
+            got[i].append(out[i])
+        live = list(range(len(reqs)))
+        k = 0
+        while live:
+            live = [i for i in live if k < plan[i][1]]
+            if not live:
+                break
+            out = eng.step([(slots[i], [reqs[i][plan[i][0] + k]], (0,)) for i in live]).cpu()
+            for j, i in enumerate(live):
+                got[i].append(out[j].clone())
+            done = [i for i in live if k + 1 >= plan[i][1]]
+            eng.close([slots[i] for i in done])                       # a shorter request ends earlier
+            live = [i for i in live if i not in done]
+            k += 1
+        for i, ids in enumerate(reqs):
+            p = plan[i][0]
+            torch.testing.assert_close(torch.stack(got[i]), ref(ids)[p - 1:], **TOL[dtype])
+    assert used_slots[1] & used_slots[0] and used_slots[2] & used_slots[0]
+    assert eng.cache.book.pages_in_use() == [0] * eng.cache.n_groups and eng.cache.book.free_slots == eng.cache.max_slots
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_long_decoding(dtype, model_folders):
+    """600 tokens decoded one by one after a short prompt: positions cross nine pages, the decode step runs
+    as a captured graph from its second occurrence on, and the window layers of C drop pages on the way."""
+    for name, total in (("D", 640), ("C", 330)):
+        eng, ref = load(model_folders[name], dtype, max_tokens=1024), oracle(model_folders[name], dtype)
+        (ids,) = requests_for(name, [total], seed=5)
+        (slot,) = eng.open(1)
+        eng.step([(slot, ids[:7], ())])
+        check = {7, 8, 63, 64, 65, 127, 128, 200, 319, 320, total - 1}
+        for t in range(7, total):
+            out = eng.step([(slot, [ids[t]], (0,))])
+            if t in check:
+                torch.testing.assert_close(out.cpu()[0], ref(ids)[t], **TOL[dtype])
+        if name == "C":
+            win = [g for g in eng.cache.book.groups if g.window][0]
+            assert (win.table[slot] >= 0).sum() <= 2          # 40 keys never need more than two pages
+        eng.close([slot])
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_first_tokens(name, dtype, model_folders):
+    eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
+    (ids,) = requests_for(name, [4], seed=9)
+    (slot,) = eng.open(1)
+    rows = [eng.step([(slot, [t], (0,))]).cpu().clone() for t in ids]       # position 0 on: no prompt step at all
+    eng.close([slot])
+    torch.testing.assert_close(torch.cat(rows), ref(ids), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_chunked_prompt_and_wanted_rows_in_any_order(dtype, model_folders):
+    """A step longer than max_step_tokens is cut into chunks; wanted places may come in any order."""
+    name = "D"
+    eng = load(model_folders[name], dtype, max_tokens=2048, max_step_tokens=96)
+    ref = oracle(model_folders[name], dtype)
+    reqs = requests_for(name, [150, 40, 97], seed=3)
+    wants = [(149, 0, 95, 96), (), (96, 5)]
+    slots = eng.open(3)
+    out = eng.step([(s, ids, w) for s, ids, w in zip(slots, reqs, wants)]).cpu()
+    eng.close(slots)
+    want_rows = torch.stack([ref(ids)[w] for ids, ws in zip(reqs, wants) for w in ws])
+    torch.testing.assert_close(out, want_rows, **TOL[dtype])
+
+
+def test_float32_is_bitwise_schedule_independent(model_folders):
+    """In float32 every kernel sums in an order that depends on the token's own position only, so a request
+    gives the same bits alone, token by token and inside a batch."""
+    name = "B"
+    eng = load(model_folders[name], "fp32")
+    reqs = requests_for(name, [50, 9, 77], seed=1)
+    alone = []
+    for ids in reqs:
+        (s,) = eng.open(1)
+        alone.append(eng.step([(s, ids, tuple(range(len(ids))))]).cpu())
+        eng.close([s])
+    slots = eng.open(3)
+    batch = eng.step([(s, ids, tuple(range(len(ids)))) for s, ids in zip(slots, reqs)]).cpu()
+    eng.close(slots)
+    assert torch.equal(batch, torch.cat(alone))
+    (s,) = eng.open(1)
+    steps = torch.cat([eng.step([(s, [t], (0,))]).cpu().clone() for t in reqs[1]])
+    eng.close([s])
+    assert torch.equal(steps, alone[1])
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(name, model_folders):
+    import sleuth_b200 as sb
+    cfg, w = plain.read_model(model_folders[name])
+    eng = load(model_folders[name], "fp32", max_tokens=512)
+    prompts = requests_for(name, [3, 12, 30, 1, 8], seed=2)
+    want = [plain.greedy_generate(cfg, w, p, 10) for p in prompts]
+    res = eng.generate(prompts, max_new_tokens=10, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=(), max_batch=3)
+    assert [r.new_ids for r in res] == want and all(r.stop_reason == "max_new_tokens" for r in res)
+    one = sb.generate(eng, prompts[1], max_new_tokens=10, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=(),
+                      cuda_graph=False)
+    assert one.new_ids == want[1] and one.prompt_ids == prompts[1] and one.decode_tok_per_s > 0
+    stop = want[2][3]
+    res = eng.generate([prompts[2]], max_new_tokens=10, sampling=sb.SamplingConfig(temperature=0.0), stop_ids={stop})
+    assert res[0].new_ids == want[2][:want[2].index(stop) + 1] and res[0].stop_reason == "stop_token"
+    # bfloat16 follows the same path; its tokens may differ at near-ties, its bookkeeping may not
+    eng16 = load(model_folders[name], "bf16", max_tokens=512)
+    r16 = eng16.generate(prompts, max_new_tokens=10, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())
+    assert all(len(r.new_ids) == 10 for r in r16)
+    agree = sum(a == b for r, ww in zip(r16, want) for a, b in zip(r.new_ids[:1], ww[:1]))
+    assert agree >= 4
+
+
+def test_context_full_through_the_entry_point(model_folders):
+    import sleuth_b200 as sb
+    eng = sb.load(model_folders["A"], dtype="fp32", max_seq_len=20, max_tokens=256)
+    res = eng.generate([[1, 2, 3] * 6, [4] * 30], max_new_tokens=50, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())
+    assert res[0].stop_reason == "context_full" and len(res[0].new_ids) == 3          # 18 + 2 fed = 20 positions
+    assert res[1].prompt_ids == [4] * 19 and res[1].stop_reason == "context_full" and len(res[1].new_ids) == 2
+
+
+def test_seeded_sampling_is_reproducible_and_batch_independent(model_folders):
+    import sleuth_b200 as sb
+    eng = load(model_folders["B"], "fp32")
+    prompts = requests_for("B", [5, 9, 14], seed=4)
+    cfg = sb.SamplingConfig(temperature=0.9, top_k=50, top_p=0.95, min_p=0.01, repetition_penalty=1.2, no_repeat_ngram=3)
+    a = eng.generate(prompts, max_new_tokens=12, sampling=cfg, seed=123, stop_ids=())
+    b = eng.generate(prompts, max_new_tokens=12, sampling=cfg, seed=123, stop_ids=(), max_batch=1)
+    c = eng.generate(prompts, max_new_tokens=12, sampling=cfg, seed=124, stop_ids=())
+    assert [r.new_ids for r in a] == [r.new_ids for r in b]
+    assert [r.new_ids for r in a] != [r.new_ids for r in c]
+    lim = eng.generate(prompts, max_new_tokens=12, sampling=sb.SamplingConfig(temperature=1.5), seed=1, stop_ids=(), vocab_limit=40)
+    assert all(t < 40 for r in lim for t in r.new_ids)
+
+
+@pytest.mark.parametrize("vocab", [503, 151936])
+def test_sampler_against_the_plain_pipeline(vocab):
+    from sleuth_b200.sampling import SamplingConfig
+    from sleuth_b200.sampling.sampler import Sampler
+    g = torch.Generator().manual_seed(vocab)
+    rows = 6
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    sampler = Sampler("cuda:0", vocab)
+    cases = [SamplingConfig(temperature=0.0), SamplingConfig(temperature=0.7), SamplingConfig(temperature=1.3, top_k=40),
+             SamplingConfig(temperature=1.0, top_p=0.8), SamplingConfig(temperature=1.1, min_p=0.05),
+             SamplingConfig(temperature=0.9, top_k=200, top_p=0.9, min_p=0.02, repetition_penalty=1.3),
+             SamplingConfig(temperature=0.0, repetition_penalty=1.5)]
+    recent = [[int(logits[r].argmax()), 3, 7] for r in range(rows)]
+    banned = [[int(logits[r].topk(2).indices[1])] if r % 2 else [] for r in range(rows)]
+    for ci, cfg in enumerate(cases):
+        for trial in range(3):
+            u = torch.rand(rows, generator=g).clamp(0, 0.999999)
+            got = sampler.to_host(sampler.choose(logits.clone().to("cuda:0"), cfg, u.numpy(), vocab_limit=vocab - 3,
+                                                 recent=recent, banned=banned))
+            for r in range(rows):
+                final = plain.final_logits(logits[r, :vocab - 3], cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p,
+                                           cfg.repetition_penalty, recent[r], banned[r])
+                want = int(final.argmax()) if cfg.greedy else plain.draw(final, float(u[r]))
+                if got[r] != want:
+                    # a draw that lands within rounding of a boundary may pick the neighbour among kept tokens
+                    p = final.double().softmax(-1)
+                    cdf = p.cumsum(-1)
+                    edge = min(abs(float(cdf[want]) - float(u[r])), abs(float(cdf[want] - p[want]) - float(u[r])))
+                    assert not cfg.greedy and edge < 1e-5 and float(p[got[r]]) > 0, (ci, trial, r, got[r], want)
+
+
+def test_missing_weights_are_reported_at_load(model_folders, tmp_path):
+    import shutil
+
+    import sleuth_b200 as sb
+    from sleuth_b200.weights import WeightError, read_safetensors, write_safetensors
+    d = tmp_path / "broken"
+    shutil.copytree(model_folders["A"], d)
+    t = read_safetensors(d / "model.safetensors")
+    del t["model.layers.0.mlp.gate_proj.weight"]
+    write_safetensors(t, d / "model.safetensors")
+    with pytest.raises(WeightError, match="missing.*gate_proj"):
+        sb.load(d, dtype="fp32")
