@@ -260,6 +260,21 @@ def run_ours(args) -> dict:
     return out
 
 
+def run_part(args) -> dict:
+    """One part of the benchmark on its own, small enough to sit under a profiler."""
+    from sleuth_b200.engine.engine import Engine
+    layers = args.layers or CONFIG["num_hidden_layers"]
+    cfg = dict(CONFIG, num_hidden_layers=layers)
+    engine = Engine.from_config(cfg, seed=0, dtype="bf16", max_seq_len=CONTEXT, max_tokens=max(args.batch, 1) * CONTEXT)
+    if args.only == "decode":
+        ms, launches, mean_ctx = decode_run(engine, args.batch, args.steps, args.warmup, seed=1)
+        return {"part": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+                "tok_per_s": round(args.batch * 1000.0 / ms, 1), "mean_context": mean_ctx, "own_launches": launches}
+    ms = prefill_run(engine, warmup=args.warmup, iters=max(1, args.steps), seed=2)
+    return {"part": "prefill", "layers": layers, "tokens": PROMPT, "ms": round(ms, 3),
+            "tflops": round(prefill_flops(cfg, PROMPT) / (ms * 1e-3) / 1e12, 1)}
+
+
 # -------------------------------------------------------------------------- reference ----
 
 def run_reference(args) -> dict:
@@ -363,13 +378,19 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="run one part only, for profiling (prints that part's numbers, not the full record)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="batch of --only decode")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this library runs on a single GPU, --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.only != "all" and args.impl == "ours":
+        out = run_part(args)
+    else:
+        out = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(out))
     return 0
 
