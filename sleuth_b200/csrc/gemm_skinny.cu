@@ -1,0 +1,174 @@
+// Matrix product for a handful of rows: C[M, N] = X[M, K] * W[N, K]^T with M <= 16, bfloat16 in, float32 accumulation.
+//
+// A decode step multiplies a few token rows by every weight matrix, so the time is the time to stream the weights
+// from memory once. The kernel is built around that: each lane fetches 16 contiguous bytes of a weight row straight
+// from global memory into the register layout the tensor core wants, every weight byte is read exactly once, and a
+// block asks for its whole weight tile before it computes, so that many loads are in flight on every SM.
+//
+// Mapping. mma.sync m16n8k16 computes D[16 x 8] += A[16 x 16] * B[16 x 8]. Rows of A are the token rows (up to 16), the
+// 8 columns of B are 8 weight rows (output features), k runs over the inner dimension. In the instruction's
+// register layout lane (g, t) holds the k indices {2t, 2t+1, 2t+8, 2t+9} of A rows g, g+8 and of B column g. The sum
+// over k does not care about order, so for a block of 32 k values lane (g, t) may instead hold the 8 consecutive
+// values 8t .. 8t+7 (one 16-byte load per row), used as two instructions' worth of operands, as long as A and B use
+// the same assignment, which they do here.
+//
+// A block owns NF * 8 output features and all of K: its 8 warps take one eighth of K each and their partial sums are
+// added through shared memory in warp order (a fixed order: the result does not depend on timing). Epilogues: store
+// bfloat16, store float32, add into a float32 matrix (the residual stream), or the gated activation
+// act = silu(gate) * up for a weight matrix holding the gate rows followed by the up rows
+// (sleuth/forge/model/mlp.py:37-40), which a block computes from matching gate and up features.
+#include "common.cuh"
+
+namespace slb {
+
+enum SkinnyMode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwiglu = 3 };
+
+struct SkinnyArgs {
+  const __nv_bfloat16* X;   // [M, K]
+  const __nv_bfloat16* W;   // [N, K]  (kSwiglu: [2 * inter, K], gate rows then up rows)
+  void* C;                  // [M, ldc]
+  int M, N, K, ldc;         // kSwiglu: N = inter (features of the output)
+};
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+constexpr int kSkinnyWarps = 8;
+constexpr int kUnroll = 4;       // blocks of 32 k values fetched before any is used
+
+template <int NF, int MODE>
+__global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyArgs a) {
+  constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
+  __shared__ float red[kSkinnyWarps][TILES][16][8 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * (NF * 8);
+  const int kb_total = a.K / 32;
+  const int per = (kb_total + kSkinnyWarps - 1) / kSkinnyWarps;
+  const int kb_begin = warp * per, kb_end = min(kb_total, kb_begin + per);
+
+  // weight row of each tile for this lane, or null beyond the matrix
+  const __nv_bfloat16* wrow[TILES];
+#pragma unroll
+  for (int f = 0; f < TILES; ++f) {
+    const int feat = n0 + (f % NF) * 8 + g;
+    const int row = (MODE == kSwiglu && f >= NF) ? a.N + feat : feat;
+    wrow[f] = feat < a.N ? a.W + (size_t)row * a.K + 8 * t : nullptr;
+  }
+  const __nv_bfloat16* xrow0 = g < a.M ? a.X + (size_t)g * a.K + 8 * t : nullptr;
+  const __nv_bfloat16* xrow1 = g + 8 < a.M ? a.X + (size_t)(g + 8) * a.K + 8 * t : nullptr;
+
+  float acc[TILES][4];
+#pragma unroll
+  for (int f = 0; f < TILES; ++f) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.0f;
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+    uint4 w[kUnroll][TILES], x0[kUnroll], x1[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const bool live = kb + u < kb_end;
+      const int off = (kb + u) * 32;
+#pragma unroll
+      for (int f = 0; f < TILES; ++f) w[u][f] = (live && wrow[f]) ? ldg16(wrow[f] + off) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const bool live = kb + u < kb_end;
+      const int off = (kb + u) * 32;
+      x0[u] = (live && xrow0) ? *reinterpret_cast<const uint4*>(xrow0 + off) : zero;
+      x1[u] = (live && xrow1) ? *reinterpret_cast<const uint4*>(xrow1 + off) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+      for (int f = 0; f < TILES; ++f) {
+        mma_16816(acc[f], x0[u].x, x1[u].x, x0[u].y, x1[u].y, w[u][f].x, w[u][f].y);
+        mma_16816(acc[f], x0[u].z, x1[u].z, x0[u].w, x1[u].w, w[u][f].z, w[u][f].w);
+      }
+    }
+  }
+
+  // accumulator layout: c0, c1 = (row g, cols 2t, 2t+1); c2, c3 = (row g+8, same cols)
+#pragma unroll
+  for (int f = 0; f < TILES; ++f) {
+    red[warp][f][g][2 * t] = acc[f][0];
+    red[warp][f][g][2 * t + 1] = acc[f][1];
+    red[warp][f][g + 8][2 * t] = acc[f][2];
+    red[warp][f][g + 8][2 * t + 1] = acc[f][3];
+  }
+  __syncthreads();
+
+  for (int idx = threadIdx.x; idx < 16 * NF * 8; idx += kSkinnyWarps * 32) {
+    const int r = idx / (NF * 8), c = idx % (NF * 8);
+    const int feat = n0 + c;
+    if (r >= a.M || feat >= a.N) continue;
+    const int f = c / 8, cc = c % 8;
+    float v = 0.0f;
+#pragma unroll
+    for (int w8 = 0; w8 < kSkinnyWarps; ++w8) v += red[w8][f][r][cc];
+    if (MODE == kSwiglu) {
+      float u = 0.0f;
+#pragma unroll
+      for (int w8 = 0; w8 < kSkinnyWarps; ++w8) u += red[w8][NF + f][r][cc];
+      v = (v / (1.0f + expf(-v))) * u;
+      reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
+    } else if (MODE == kStoreBf16) {
+      reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
+    } else if (MODE == kStoreF32) {
+      reinterpret_cast<float*>(a.C)[(size_t)r * a.ldc + feat] = v;
+    } else {
+      reinterpret_cast<float*>(a.C)[(size_t)r * a.ldc + feat] += v;
+    }
+  }
+}
+
+template <int NF>
+static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
+  const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
+  const int threads = kSkinnyWarps * 32;
+  switch (mode) {
+    case kStoreBf16: gemm_skinny_kernel<NF, kStoreBf16><<<blocks, threads, 0, s>>>(a); break;
+    case kStoreF32: gemm_skinny_kernel<NF, kStoreF32><<<blocks, threads, 0, s>>>(a); break;
+    case kAddF32: gemm_skinny_kernel<NF, kAddF32><<<blocks, threads, 0, s>>>(a); break;
+    default: gemm_skinny_kernel<NF, kSwiglu><<<blocks, threads, 0, s>>>(a); break;
+  }
+  return check_launch("gemm_skinny");
+}
+
+}  // namespace slb
+
+using namespace slb;
+
+// 1 when the skinny kernel takes this problem (the caller otherwise uses the library product).
+extern "C" int slb_gemm_skinny_supported(int M, int N, int K) {
+  return M >= 1 && M <= 16 && K >= 32 && K % 32 == 0 && N >= 1;
+}
+
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds 2 * N rows, C is [M, N]).
+extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
+                               void* stream) {
+  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
+              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
+  SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: X and W must be 16-byte aligned");
+  SkinnyArgs a;
+  a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  cudaStream_t s = (cudaStream_t)stream;
+  // wide matrices: 16 or 32 features per block; narrow ones: 8, so that enough blocks exist to fill the GPU
+  if (mode == kSwiglu) return N >= 4096 ? launch_skinny<2>(a, mode, s) : launch_skinny<1>(a, mode, s);
+  if (N >= 32768) return launch_skinny<4>(a, mode, s);
+  if (N >= 4096) return launch_skinny<2>(a, mode, s);
+  return launch_skinny<1>(a, mode, s);
+}

@@ -58,14 +58,24 @@ __global__ void penalize_kernel(float* logits, long long ld, int limit, const in
   }
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, long long ld, int limit, int* __restrict__ out) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
-  const float* row = logits + (size_t)blockIdx.x * ld;
+// Argmax in two stages so that a few rows still use the whole GPU: kArgmaxChunks blocks per row each find the
+// best (value, lowest index) of their slice, then one warp per row picks among the slices. Ties go to the lowest
+// index at both stages (sampling.py:104-105 with torch.argmax's first-index rule, tests/test_generate.py:96-104).
+constexpr int kArgmaxChunks = 64;
+constexpr int kArgmaxThreads = 256;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_partial_kernel(const float* __restrict__ logits, long long ld, int limit, float* __restrict__ part_v,
+                      int* __restrict__ part_i) {
+  __shared__ float best_v[8];
+  __shared__ int best_i[8];
+  const int r = blockIdx.y, chunk = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const int per = (limit + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int begin = chunk * per, end = min(limit, begin + per);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < limit; i += blockDim.x) {
+  for (int i = begin + threadIdx.x; i < end; i += kArgmaxThreads) {
     const float v = row[i];
     if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
   }
@@ -78,16 +88,33 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int limit, int* __
   if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
   __syncthreads();
   if (warp == 0) {
-    const int nw = blockDim.x >> 5;
-    bv = lane < nw ? best_v[lane] : -INFINITY;
-    bi = lane < nw ? best_i[lane] : 0x7fffffff;
+    bv = lane < kArgmaxThreads / 32 ? best_v[lane] : -INFINITY;
+    bi = lane < kArgmaxThreads / 32 ? best_i[lane] : 0x7fffffff;
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;   // a row of NaNs picks token 0
+    if (lane == 0) { part_v[r * kArgmaxChunks + chunk] = bv; part_i[r * kArgmaxChunks + chunk] = bi; }
   }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < kArgmaxChunks; c += 32) {
+    const float v = part_v[r * kArgmaxChunks + c];
+    const int i = part_i[r * kArgmaxChunks + c];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;   // a row of NaNs picks token 0
 }
 
 struct SampleShared {
@@ -249,10 +276,22 @@ extern "C" int slb_penalize(float* logits, long long ld, int rows, int limit, co
   return check_launch("penalize");
 }
 
-extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit, int* out, void* stream) {
-  SLB_REQUIRE(rows >= 0 && limit > 0 && ld >= limit, "argmax: rows=%d limit=%d ld=%lld", rows, limit, ld);
+// scratch: 2 * rows * 64 four-byte words (slb_argmax_scratch_words), written and read within the call.
+extern "C" long long slb_argmax_scratch_words(int rows) { return 2ll * rows * kArgmaxChunks; }
+
+extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit, int* out, void* scratch,
+                          long long scratch_words, void* stream) {
+  SLB_REQUIRE(rows >= 0 && rows < 65536 && limit > 0 && ld >= limit, "argmax: rows=%d limit=%d ld=%lld", rows, limit, ld);
+  SLB_REQUIRE(scratch != nullptr && scratch_words >= slb_argmax_scratch_words(rows),
+              "argmax: %lld words of scratch memory are needed, %lld were given", slb_argmax_scratch_words(rows), scratch_words);
   if (rows == 0) return 0;
-  argmax_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, ld, limit, out);
+  float* part_v = (float*)scratch;
+  int* part_i = (int*)scratch + (size_t)rows * kArgmaxChunks;
+  cudaStream_t s = (cudaStream_t)stream;
+  argmax_partial_kernel<<<dim3(kArgmaxChunks, rows), kArgmaxThreads, 0, s>>>(logits, ld, limit, part_v, part_i);
+  int rc = check_launch("argmax (slices)");
+  if (rc) return rc;
+  argmax_final_kernel<<<rows, 32, 0, s>>>(part_v, part_i, out);
   return check_launch("argmax");
 }
 

@@ -136,9 +136,10 @@ _SIGNATURES = {
     "slb_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "slb_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P],
+    "slb_gemm_skinny": [P, P, P, I, I, I, I, I, P],
     "slb_gemm_f32": [P, P, P, P, I, I, I, I, I, I, I, P],
     "slb_penalize": [P, L, I, I, P, P, I, F, P, P, I, P],
-    "slb_argmax": [P, L, I, I, P, P],
+    "slb_argmax": [P, L, I, I, P, P, L, P],
     "slb_sample": [P, L, I, I, F, I, F, F, P, P, P],
 }
 

@@ -175,6 +175,27 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, acc
                stream if stream is not None else current_stream())
 
 
+SKINNY_MODES = {"bf16": 0, "f32": 1, "add": 2, "swiglu": 3}
+
+
+def skinny_supported(M: int, N: int, K: int) -> bool:
+    """Whether the few-rows bfloat16 product kernel takes this problem."""
+    return 1 <= M <= 16 and K >= 32 and K % 32 == 0 and N >= 1
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None) -> None:
+    """out = x[M, K] @ w^T for M <= 16 (bfloat16 in, float32 accumulation). mode: "bf16" / "f32" store,
+    "add" adds into a float32 ``out``, "swiglu" takes w = [gate rows; up rows] and stores silu(gate) * up."""
+    _cuda(x, w, out)
+    M, K = x.shape
+    N = out.shape[1]
+    _need(x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape[0] == M, "gemm_skinny: shapes or dtypes")
+    _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny: weight rows")
+    _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny: output dtype")
+    lib().call("slb_gemm_skinny", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode],
+               stream if stream is not None else current_stream())
+
+
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:
     _cuda(logits, recent, n_recent, banned, n_banned)
     R = logits.shape[0]
@@ -183,10 +204,16 @@ def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_ban
                0 if banned is None else banned.shape[1], stream if stream is not None else current_stream())
 
 
-def argmax(logits: torch.Tensor, limit: int, out: torch.Tensor, stream=None) -> None:
+def argmax_scratch_words(rows: int) -> int:
+    return 2 * rows * 64
+
+
+def argmax(logits: torch.Tensor, limit: int, out: torch.Tensor, scratch: torch.Tensor, stream=None) -> None:
+    """out[r] = first index of the largest of logits[r, :limit]. ``scratch``: int32, ``argmax_scratch_words(rows)`` long."""
     _need(logits.is_cuda and out.is_cuda and logits.dtype == torch.float32 and out.dtype == torch.int32, "argmax: dtypes")
     _need(logits.stride(1) == 1 and out.numel() >= logits.shape[0] and 0 < limit <= logits.shape[1], "argmax: shapes")
-    lib().call("slb_argmax", _p(logits), logits.stride(0), logits.shape[0], limit, _p(out),
+    _need(scratch.is_cuda and scratch.dtype == torch.int32, "argmax: scratch is an int32 CUDA tensor")
+    lib().call("slb_argmax", _p(logits), logits.stride(0), logits.shape[0], limit, _p(out), _p(scratch), scratch.numel(),
                stream if stream is not None else current_stream())
 
 

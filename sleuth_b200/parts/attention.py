@@ -100,7 +100,7 @@ class GQAAttention(Part):
         else:
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
                                   s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
-        self.o.forward(y, into=x, stream=b.stream)
+        self.o.forward(y, into=x, ws=ws, stream=b.stream)
         ws.release(mark)
 
 

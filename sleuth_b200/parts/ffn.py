@@ -31,10 +31,13 @@ class GatedMLP(Part):
     def forward(self, h, x, b, ws):
         T = h.shape[0]
         mark = ws.mark()
-        gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
-        ops.swiglu(gu, act, b.stream)
-        self.down.forward(act, into=x, stream=b.stream)
+        if self.ctx.dtype == torch.bfloat16 and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden):
+            ops.gemm_skinny(h, self.gate_up.weight, act, "swiglu", b.stream)      # activation in the product's epilogue
+        else:
+            gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
+            ops.swiglu(gu, act, b.stream)
+        self.down.forward(act, into=x, ws=ws, stream=b.stream)
         ws.release(mark)
 
 

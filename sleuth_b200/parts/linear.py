@@ -2,8 +2,10 @@
 
 * float32 run: the package's own FMA kernel (``csrc/gemm_f32.cu``); no tensor-core mode, and every
   output element sums over k in one fixed order whatever the number of rows.
-* bfloat16 run: a library product with float32 accumulation (cuBLAS through ``torch.mm``), as the
-  reference's ``nn.Linear`` (sleuth/forge/model/attention.py:106-108).
+* bfloat16 run, up to 16 rows (decode steps): the package's weight-streaming tensor-core kernel
+  (``csrc/gemm_skinny.cu``), with the residual add or the float32 store in its epilogue.
+* bfloat16 run, more rows: a library product with float32 accumulation (cuBLAS through ``torch.mm``),
+  as the reference's ``nn.Linear`` (sleuth/forge/model/attention.py:106-108).
 
 ``into`` adds the product to a float32 tensor (the residual stream) instead of returning it.
 """
@@ -61,6 +63,15 @@ class Linear:
             if out is None:
                 out = ws.take((M, self.out_features), torch.float32)
             ops.gemm_f32(h, self.weight, out, stream=stream)
+            return out
+        if ops.skinny_supported(M, self.out_features, self.in_features):
+            if into is not None:
+                ops.gemm_skinny(h, self.weight, into, "add", stream)
+                return into
+            want = out_dtype or (out.dtype if out is not None else self.dtype)
+            if out is None:
+                out = ws.take((M, self.out_features), want)
+            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream)
             return out
         if into is not None:
             mode = _accumulate_mode(h.device)

@@ -20,11 +20,13 @@ class Sampler:
         self.vocab = vocab
         self._out = torch.zeros(1024, dtype=torch.int32, device=self.device)
         self._host = torch.zeros(1024, dtype=torch.int32).pin_memory()
+        self._scratch = torch.zeros(ops.argmax_scratch_words(1024), dtype=torch.int32, device=self.device)
 
     def _fit(self, n: int) -> None:
         if n > self._out.numel():
             self._out = torch.zeros(2 * n, dtype=torch.int32, device=self.device)
             self._host = torch.zeros(2 * n, dtype=torch.int32).pin_memory()
+            self._scratch = torch.zeros(ops.argmax_scratch_words(2 * n), dtype=torch.int32, device=self.device)
 
     def choose(self, logits: torch.Tensor, cfg: SamplingConfig, uniform: torch.Tensor | np.ndarray | None = None,
                vocab_limit: int | None = None, recent: list[list[int]] | None = None,
@@ -49,7 +51,7 @@ class Sampler:
             ops.penalize(logits, limit, rec_t, nrec_t, cfg.repetition_penalty, ban_t, nban_t, stream)
         out = self._out[:n]
         if cfg.greedy:
-            ops.argmax(logits, limit, out, stream)
+            ops.argmax(logits, limit, out, self._scratch, stream)
         else:
             if uniform is None:
                 raise ValueError("sampling with a temperature needs one uniform number per row")

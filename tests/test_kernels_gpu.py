@@ -264,3 +264,66 @@ def test_qkv_post(dtype, heads, kv_heads, hd, rot):
         page = int(table[tok_seq[t], tok_pos[t] // 64])
         torch.testing.assert_close(kp[page, :, tok_pos[t] % 64], k_ref[t], **tl)
         torch.testing.assert_close(vp[page, :, tok_pos[t] % 64], v_ref[t], **tl)
+
+
+# ------------------------------------------------------------------ few-rows product ----
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(1024, 1024), (1000, 2048), (4096, 1024), (40, 96), (33000, 64), (1024, 3072)])
+def test_gemm_skinny(M, N, K):
+    o = ops()
+    assert o.skinny_supported(M, N, K)
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for mode, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        out = torch.full((M, N), float("nan"), dtype=dt, device=DEV)
+        o.gemm_skinny(x.to(DEV), w.to(DEV), out, mode)
+        torch.testing.assert_close(out.cpu().double(), ref, rtol=1e-2 if dt == torch.bfloat16 else 1e-4,
+                                   atol=1e-2 if dt == torch.bfloat16 else 1e-4)
+    base = torch.randn(M, N, generator=g)
+    acc = base.clone().to(DEV)
+    o.gemm_skinny(x.to(DEV), w.to(DEV), acc, "add")
+    torch.testing.assert_close(acc.cpu().double(), base.double() + ref, rtol=1e-4, atol=1e-4)
+    # twice the same call gives the same bits (the warps' partial sums are added in a fixed order)
+    again = base.clone().to(DEV)
+    o.gemm_skinny(x.to(DEV), w.to(DEV), again, "add")
+    assert torch.equal(acc, again)
+
+
+@pytest.mark.parametrize("M,inter,K", [(1, 3072, 1024), (8, 200, 64), (16, 4100, 128), (5, 136, 96)])
+def test_gemm_skinny_gated_activation(M, inter, K):
+    o = ops()
+    g = torch.Generator().manual_seed(inter)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, generator=g) / math.sqrt(K) * 2).to(torch.bfloat16)
+    gate, up = x.double() @ w[:inter].double().T, x.double() @ w[inter:].double().T
+    act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemm_skinny(x.to(DEV), w.to(DEV), act, "swiglu")
+    torch.testing.assert_close(act.cpu().double(), gate * torch.sigmoid(gate) * up, rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_skinny_refuses_what_it_cannot_run():
+    o = ops()
+    assert not o.skinny_supported(17, 64, 64) and not o.skinny_supported(4, 64, 40)
+    x = torch.zeros(4, 40, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="multiple of 32"):
+        o.gemm_skinny(x, torch.zeros(8, 40, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV), "bf16")
+
+
+@pytest.mark.parametrize("rows,vocab,limit", [(1, 503, 503), (5, 151936, 151936), (64, 1000, 777), (3, 70, 64)])
+def test_argmax_first_index_on_ties(rows, vocab, limit):
+    o = ops()
+    g = torch.Generator().manual_seed(rows)
+    logits = torch.randn(rows, vocab, generator=g)
+    logits[0, limit // 3] = 50.0
+    logits[0, limit - 1] = 50.0                      # a tie: the lower index wins
+    if rows > 1:
+        logits[1, limit:] = 99.0                     # beyond the limit: never chosen
+        logits[1, 5] = logits[1, :limit].max()       # ties with a later maximum
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(o.argmax_scratch_words(rows), dtype=torch.int32, device=DEV)
+    o.argmax(logits.to(DEV), limit, out, scratch)
+    want = [int(torch.nonzero(r[:limit] == r[:limit].max())[0]) for r in logits]
+    assert out.cpu().tolist() == want
