@@ -100,6 +100,7 @@ constexpr int kFlashThreads = 128;
 // ------------------------------------------------------------------------------------ prefill ----
 template <int HD>
 __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a) {
+  pdl_enter();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;            // bytes of one [64][HD] tile
   const uint32_t sQ = smem_u32(smem);
@@ -283,6 +284,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
 // grid: (splits * row_tiles, kv_heads, sequences); every sequence has count 1.
 template <int HD>
 __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
+  pdl_enter();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;
   const uint32_t sK = smem_u32(smem), sV = sK + 2 * TILE;
@@ -463,6 +465,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_start, int heads,
                                     int splits, int hd) {
+  pdl_enter();
   const int seq = blockIdx.x / heads, head = blockIdx.x % heads, d = threadIdx.x;
   const size_t base = ((size_t)seq * heads + head) * splits;
   float m = -INFINITY;
@@ -489,7 +492,7 @@ static int launch_prefill(const FlashArgs& a, int n_seqs, int max_count, cudaStr
     configured = true;
   }
   dim3 grid(tiles, a.kv_heads, n_seqs);
-  attn_prefill_kernel<HD><<<grid, kFlashThreads, smem, s>>>(a);
+  launch(attn_prefill_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
   return check_launch("attention (prefill)");
 }
 
@@ -507,10 +510,10 @@ static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
     configured = true;
   }
   dim3 grid(a.splits * row_tiles, a.kv_heads, n_seqs);
-  attn_decode_kernel<HD><<<grid, kFlashThreads, smem, s>>>(a);
+  launch(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
   int rc = check_launch("attention (decode)");
   if (rc || a.splits == 1) return rc;
-  attn_combine_kernel<<<n_seqs * a.heads, HD, 0, s>>>(a.part_o, a.part_ml, a.out, a.seq_start, a.heads, a.splits, HD);
+  launch(attn_combine_kernel, dim3(n_seqs * a.heads), dim3(HD), 0, s, a.part_o, a.part_ml, a.out, a.seq_start, a.heads, a.splits, HD);
   return check_launch("attention (combine)");
 }
 

@@ -75,6 +75,7 @@ constexpr int kAttnWarps = 4;
 
 template <typename T, int PER_LANE>
 __global__ void attn_generic_kernel(AttnArgs a) {
+  pdl_enter();
   __shared__ float q_all[kAttnWarps][256];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * kAttnWarps + warp;
@@ -146,11 +147,11 @@ static int launch_attn_generic(const AttnArgs& a, cudaStream_t s) {
   const int per_lane = (a.head_dim + 31) / 32;
   const int threads = kAttnWarps * 32;
   switch (per_lane) {
-    case 1: attn_generic_kernel<T, 1><<<(int)blocks, threads, 0, s>>>(a); break;
-    case 2: attn_generic_kernel<T, 2><<<(int)blocks, threads, 0, s>>>(a); break;
-    case 3: attn_generic_kernel<T, 3><<<(int)blocks, threads, 0, s>>>(a); break;
-    case 4: attn_generic_kernel<T, 4><<<(int)blocks, threads, 0, s>>>(a); break;
-    default: attn_generic_kernel<T, 8><<<(int)blocks, threads, 0, s>>>(a); break;
+    case 1: launch(attn_generic_kernel<T, 1>, dim3((int)blocks), dim3(threads), 0, s, a); break;
+    case 2: launch(attn_generic_kernel<T, 2>, dim3((int)blocks), dim3(threads), 0, s, a); break;
+    case 3: launch(attn_generic_kernel<T, 3>, dim3((int)blocks), dim3(threads), 0, s, a); break;
+    case 4: launch(attn_generic_kernel<T, 4>, dim3((int)blocks), dim3(threads), 0, s, a); break;
+    default: launch(attn_generic_kernel<T, 8>, dim3((int)blocks), dim3(threads), 0, s, a); break;
   }
   return check_launch("attention (general kernel)");
 }

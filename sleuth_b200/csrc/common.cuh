@@ -27,6 +27,39 @@ int check_launch(const char* what);
     if (!(cond)) return slb::fail(1, __VA_ARGS__); \
   } while (0)
 
+// Programmatic dependent launch. Every kernel of this library is launched with the stream-serialization
+// attribute (unless slb_set_pdl(0) turned it off): it may then begin while the kernel before it in the stream is
+// still running. A kernel first lets its own successor start (pdl_launch_dependents), may fetch data that no
+// kernel writes (weights), and must call pdl_wait() before it reads or writes anything else: the wait returns
+// when the preceding kernel has completed and its writes are visible. Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+bool pdl_enabled();
+void note_launch_error(cudaError_t e);
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) note_launch_error(e);
+  return e;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -8,6 +8,7 @@ namespace slb {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
                              int dim, float scale) {
+  pdl_enter();
   const int t = blockIdx.x;
   const TW* row = table + (size_t)ids[t] * dim;
   float* out = x + (size_t)t * dim;
@@ -20,6 +21,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int dim, float eps) {
+  pdl_enter();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
@@ -34,9 +36,52 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>((xr[i] * inv) * w[i]);
 }
 
+// The same for widths that are multiples of 4: 16-byte loads, the row kept in registers between the two passes.
+template <typename TO, int PER_THREAD>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int dim, float eps) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
+  const int n4 = dim >> 2;
+  float4 v[PER_THREAD];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[i].x, v[i].x, ss);
+    ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss);
+    ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  TO* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c >= n4) continue;
+    const float4 g = w4[c];
+    const float a = (v[i].x * inv) * g.x, b = (v[i].y * inv) * g.y, cc = (v[i].z * inv) * g.z, d = (v[i].w * inv) * g.w;
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(o)[c] = make_float4(a, b, cc, d);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(o)[c] = pk;
+    }
+  }
+}
+
 // x += delta (delta in the activation dtype), float32 sum.
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+  pdl_enter();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t step = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += step) x[i] += to_f32(delta[i]);
@@ -46,6 +91,7 @@ __global__ void add_kernel(float* __restrict__ x, const TD* __restrict__ delta, 
 // (sleuth/forge/model/mlp.py:37-40.)
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total) {
+  pdl_enter();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t step = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
@@ -53,6 +99,31 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
     const float g = to_f32(gu[t * 2 * inter + j]);
     const float u = to_f32(gu[t * 2 * inter + inter + j]);
     act[i] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+// bfloat16, inter a multiple of 8: 16 bytes of gate and of up per thread.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int inter,
+                                     size_t total8) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  const int per_row = inter >> 3;
+  for (; i < total8; i += step) {
+    const size_t t = i / per_row, j = (i - t * per_row) << 3;
+    const Bf16x8 g = *reinterpret_cast<const Bf16x8*>(gu + t * 2 * inter + j);
+    const Bf16x8 u = *reinterpret_cast<const Bf16x8*>(gu + t * 2 * inter + inter + j);
+    float gf[8], uf[8];
+    unpack8(g, gf);
+    unpack8(u, uf);
+    Bf16x8 o;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float a = (gf[2 * e] / (1.0f + expf(-gf[2 * e]))) * uf[2 * e];
+      const float b = (gf[2 * e + 1] / (1.0f + expf(-gf[2 * e + 1]))) * uf[2 * e + 1];
+      o.v[e] = __floats2bfloat162_rn(a, b);
+    }
+    *reinterpret_cast<Bf16x8*>(act + t * inter + j) = o;
   }
 }
 
@@ -73,9 +144,9 @@ extern "C" int slb_embed(const int* ids, const void* table, int table_dtype, flo
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = dim >= 256 ? 256 : 64;
   if (table_dtype == kF32)
-    embed_kernel<float><<<tokens, threads, 0, s>>>(ids, (const float*)table, x, dim, scale);
+    launch(embed_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, (const float*)table, x, dim, scale);
   else if (table_dtype == kBF16)
-    embed_kernel<__nv_bfloat16><<<tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, x, dim, scale);
+    launch(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, x, dim, scale);
   else
     return fail(1, "embed: unknown dtype %d", table_dtype);
   return check_launch("embed");
@@ -86,13 +157,23 @@ extern "C" int slb_rmsnorm(const float* x, const float* w, void* out, int out_dt
   SLB_REQUIRE(n_rows >= 0 && dim > 0 && eps > 0.0f, "rmsnorm: rows=%d dim=%d eps=%g", n_rows, dim, (double)eps);
   if (n_rows == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  SLB_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "rmsnorm: unknown dtype %d", out_dtype);
+  if (dim % 4 == 0 && dim <= 8192 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+    const int n4 = dim / 4;
+    const int threads = n4 <= 64 ? 64 : (n4 <= 128 ? 128 : 256);
+    const int per = (n4 + threads - 1) / threads;      // at most 8
+    #define SLB_NORM(P)                                                                                              \
+      if (out_dtype == kF32) launch(rmsnorm_vec_kernel<float, P>, dim3(n_rows), dim3(threads), 0, s, x, w, (float*)out, rows, dim, eps); \
+      else launch(rmsnorm_vec_kernel<__nv_bfloat16, P>, dim3(n_rows), dim3(threads), 0, s, x, w, (__nv_bfloat16*)out, rows, dim, eps)
+    if (per <= 1) { SLB_NORM(1); } else if (per <= 2) { SLB_NORM(2); } else if (per <= 4) { SLB_NORM(4); } else { SLB_NORM(8); }
+    #undef SLB_NORM
+    return check_launch("rmsnorm");
+  }
   const int threads = norm_threads(dim);
   if (out_dtype == kF32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(x, w, (float*)out, rows, dim, eps);
-  else if (out_dtype == kBF16)
-    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, w, (__nv_bfloat16*)out, rows, dim, eps);
+    launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, w, (float*)out, rows, dim, eps);
   else
-    return fail(1, "rmsnorm: unknown dtype %d", out_dtype);
+    launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, x, w, (__nv_bfloat16*)out, rows, dim, eps);
   return check_launch("rmsnorm");
 }
 
@@ -104,9 +185,9 @@ extern "C" int slb_add(float* x, const void* delta, int delta_dtype, long long n
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (delta_dtype == kF32)
-    add_kernel<float><<<(int)blocks, threads, 0, s>>>(x, (const float*)delta, (size_t)n);
+    launch(add_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, x, (const float*)delta, (size_t)n);
   else if (delta_dtype == kBF16)
-    add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    launch(add_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, x, (const __nv_bfloat16*)delta, (size_t)n);
   else
     return fail(1, "add: unknown dtype %d", delta_dtype);
   return check_launch("add");
@@ -120,10 +201,17 @@ extern "C" int slb_swiglu(const void* gu, void* act, int dtype, int tokens, int 
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == kBF16 && inter % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)act % 16 == 0)) {
+    const size_t total8 = total / 8;
+    size_t b8 = (total8 + threads - 1) / threads;
+    if (b8 > 148 * 32) b8 = 148 * 32;
+    launch(swiglu_bf16x8_kernel, dim3((int)b8), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inter, total8);
+    return check_launch("swiglu");
+  }
   if (dtype == kF32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)act, inter, total);
+    launch(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inter, total);
   else if (dtype == kBF16)
-    swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act,
+    launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act,
                                                                inter, total);
   else
     return fail(1, "swiglu: unknown dtype %d", dtype);

@@ -1,6 +1,7 @@
 // Error reporting shared by every launcher: a message per host thread, read through slb_last_error().
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -16,8 +17,24 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static int g_pdl = -1;
+
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("SLEUTH_B200_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl == 1;
+}
+
+static thread_local cudaError_t g_launch_error = cudaSuccess;
+
+void note_launch_error(cudaError_t e) { g_launch_error = e; }
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = g_launch_error;
+  g_launch_error = cudaSuccess;
   if (e != cudaSuccess) return fail(2, "%s: launch failed: %s", what, cudaGetErrorString(e));
   return 0;
 }
@@ -27,3 +44,7 @@ int check_launch(const char* what) {
 extern "C" const char* slb_last_error() { return slb::g_message; }
 
 extern "C" int slb_abi_version() { return 1; }
+
+// 1: kernels may start while their predecessor still runs (programmatic dependent launch); 0: strictly one after another.
+extern "C" void slb_set_pdl(int on) { slb::g_pdl = on ? 1 : 0; }
+extern "C" int slb_get_pdl() { return slb::pdl_enabled() ? 1 : 0; }

@@ -16,6 +16,7 @@ template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                 float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, int accumulate) {
+  pdl_enter();
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[kBK][BM + 1];
   __shared__ float Ws[kBK][BN + 1];
@@ -86,12 +87,12 @@ extern "C" int slb_gemm_f32(const float* A, const float* W, const float* bias, f
   if (M <= 16) {
     constexpr int BM = 16, BN = 32;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_f32_kernel<BM, BN, 1, 2><<<grid, 256, 0, s>>>(A, W, bias, C, M, N, K, lda, ldw, ldc, accumulate);
+    launch(gemm_f32_kernel<BM, BN, 1, 2>, dim3(grid), dim3(256), 0, s, A, W, bias, C, M, N, K, lda, ldw, ldc, accumulate);
   } else {
     constexpr int BM = 64, BN = 64;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     SLB_REQUIRE(grid.y < 65536, "gemm_f32: M=%d needs more than 65535 row tiles", M);
-    gemm_f32_kernel<BM, BN, 4, 4><<<grid, 256, 0, s>>>(A, W, bias, C, M, N, K, lda, ldw, ldc, accumulate);
+    launch(gemm_f32_kernel<BM, BN, 4, 4>, dim3(grid), dim3(256), 0, s, A, W, bias, C, M, N, K, lda, ldw, ldc, accumulate);
   }
   return check_launch("gemm_f32");
 }

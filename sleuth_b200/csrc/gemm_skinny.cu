@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
   for (int f = 0; f < TILES; ++f) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.0f;
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
-    uint4 w[kUnroll][TILES], x0[kUnroll], x1[kUnroll];
+  uint4 w[kUnroll][TILES];
+  auto fetch_weights = [&](int kb) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const bool live = kb + u < kb_end;
@@ -83,6 +83,15 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
 #pragma unroll
       for (int f = 0; f < TILES; ++f) w[u][f] = (live && wrow[f]) ? ldg16(wrow[f] + off) : zero;
     }
+  };
+  // Weights are written by no kernel, so the first batch of loads goes out before the wait for the kernel that
+  // produces X: the memory system is already streaming this layer's weights while the previous kernel finishes.
+  pdl_launch_dependents();
+  fetch_weights(kb_begin);
+  pdl_wait();
+  for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+    if (kb != kb_begin) fetch_weights(kb);
+    uint4 x0[kUnroll], x1[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const bool live = kb + u < kb_end;
@@ -139,10 +148,10 @@ static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
   const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
   const int threads = kSkinnyWarps * 32;
   switch (mode) {
-    case kStoreBf16: gemm_skinny_kernel<NF, kStoreBf16><<<blocks, threads, 0, s>>>(a); break;
-    case kStoreF32: gemm_skinny_kernel<NF, kStoreF32><<<blocks, threads, 0, s>>>(a); break;
-    case kAddF32: gemm_skinny_kernel<NF, kAddF32><<<blocks, threads, 0, s>>>(a); break;
-    default: gemm_skinny_kernel<NF, kSwiglu><<<blocks, threads, 0, s>>>(a); break;
+    case kStoreBf16: launch(gemm_skinny_kernel<NF, kStoreBf16>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreF32: launch(gemm_skinny_kernel<NF, kStoreF32>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kAddF32: launch(gemm_skinny_kernel<NF, kAddF32>, dim3(blocks), dim3(threads), 0, s, a); break;
+    default: launch(gemm_skinny_kernel<NF, kSwiglu>, dim3(blocks), dim3(threads), 0, s, a); break;
   }
   return check_launch("gemm_skinny");
 }

@@ -36,6 +36,7 @@ struct QkvPostArgs {
 
 template <typename T, int PER_LANE>
 __global__ void qkv_post_kernel(QkvPostArgs a) {
+  pdl_enter();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int rows_per_token = a.heads + 2 * a.kv_heads;
@@ -122,19 +123,96 @@ __global__ void qkv_post_kernel(QkvPostArgs a) {
   }
 }
 
+// Head sizes 64, 128 and 256 with the whole head rotated (or none of it): lane l holds the EPL = head_dim / 32
+// contiguous channels l * EPL .., one vector load and store per lane, and a channel's rotation partner
+// (head_dim / 2 away) sits at the same place in lane l ^ 16, so a shuffle replaces the shared-memory staging.
+template <typename T, int EPL>
+struct alignas(sizeof(T) * EPL) LaneVec {
+  T v[EPL];
+};
+
+template <typename T, int EPL>
+__global__ void qkv_post_vec_kernel(QkvPostArgs a) {
+  pdl_enter();
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rows_per_token = a.heads + 2 * a.kv_heads;
+  const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (item >= (long long)a.tokens * rows_per_token) return;
+  const int t = (int)(item / rows_per_token);
+  const int r = (int)(item - (long long)t * rows_per_token);
+  constexpr int HD = 32 * EPL;
+  const int c0 = lane * EPL;
+
+  const LaneVec<T, EPL> in = *reinterpret_cast<const LaneVec<T, EPL>*>(
+      (const T*)a.qkv + ((size_t)t * rows_per_token + r) * HD + c0);
+  float v[EPL];
+  float ss = 0.0f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    float x = to_f32(in.v[e]);
+    if (a.bias) x += a.bias[(size_t)r * HD + c0 + e];
+    v[e] = x;
+    ss = fmaf(x, x, ss);
+  }
+  const bool is_q = r < a.heads;
+  const bool is_k = !is_q && r < a.heads + a.kv_heads;
+  const float* gain = is_q ? a.q_gain : (is_k ? a.k_gain : nullptr);
+  const int pos = a.tok_pos[t];
+  if (is_q || is_k) {
+    if (gain) {
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[e] = (v[e] * inv) * gain[c0 + e];
+    }
+    if (a.cos_table) {
+      const float* cs = a.cos_table + (size_t)pos * (HD / 2) + (lane & 15) * EPL;
+      const float* sn = a.sin_table + (size_t)pos * (HD / 2) + (lane & 15) * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float partner = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        const float other = lane < 16 ? -partner : partner;
+        v[e] = v[e] * cs[e] + other * sn[e];
+      }
+    }
+  }
+  T* dst;
+  if (is_q) {
+    dst = (T*)a.q_out + ((size_t)t * a.heads + r) * HD;
+  } else {
+    if (a.k_pool == nullptr) return;
+    const int kh = is_k ? r - a.heads : r - a.heads - a.kv_heads;
+    const int page = a.block_table[(size_t)a.tok_seq[t] * a.table_stride + pos / kPageTokens];
+    T* pool = (T*)(is_k ? a.k_pool : a.v_pool);
+    dst = pool + (((size_t)page * a.kv_heads + kh) * kPageTokens + (pos % kPageTokens)) * HD;
+  }
+  LaneVec<T, EPL> out;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) out.v[e] = from_f32<T>(v[e]);
+  *reinterpret_cast<LaneVec<T, EPL>*>(dst + c0) = out;
+}
+
 template <typename T>
 static int launch_qkv_post(const QkvPostArgs& a, cudaStream_t s) {
   const long long items = (long long)a.tokens * (a.heads + 2 * a.kv_heads);
   const int warps = 8;
   const long long blocks = (items + warps - 1) / warps;
   SLB_REQUIRE(blocks < (1ll << 31), "qkv_post: too many rows (%lld)", items);
+  const bool whole = a.cos_table == nullptr || a.rot_dim == a.head_dim;
+  if (whole && (a.head_dim == 64 || a.head_dim == 128 || a.head_dim == 256) && ((uintptr_t)a.qkv % 16 == 0)) {
+    if (a.head_dim == 64) launch(qkv_post_vec_kernel<T, 2>, dim3((int)blocks), dim3(warps * 32), 0, s, a);
+    else if (a.head_dim == 128) launch(qkv_post_vec_kernel<T, 4>, dim3((int)blocks), dim3(warps * 32), 0, s, a);
+    else launch(qkv_post_vec_kernel<T, 8>, dim3((int)blocks), dim3(warps * 32), 0, s, a);
+    return check_launch("qkv_post");
+  }
   const int per_lane = (a.head_dim + 31) / 32;
   switch (per_lane) {
-    case 1: qkv_post_kernel<T, 1><<<(int)blocks, warps * 32, 0, s>>>(a); break;
-    case 2: qkv_post_kernel<T, 2><<<(int)blocks, warps * 32, 0, s>>>(a); break;
-    case 3: qkv_post_kernel<T, 3><<<(int)blocks, warps * 32, 0, s>>>(a); break;
-    case 4: qkv_post_kernel<T, 4><<<(int)blocks, warps * 32, 0, s>>>(a); break;
-    default: qkv_post_kernel<T, 8><<<(int)blocks, warps * 32, 0, s>>>(a); break;
+    case 1: launch(qkv_post_kernel<T, 1>, dim3((int)blocks), dim3(warps * 32), 0, s, a); break;
+    case 2: launch(qkv_post_kernel<T, 2>, dim3((int)blocks), dim3(warps * 32), 0, s, a); break;
+    case 3: launch(qkv_post_kernel<T, 3>, dim3((int)blocks), dim3(warps * 32), 0, s, a); break;
+    case 4: launch(qkv_post_kernel<T, 4>, dim3((int)blocks), dim3(warps * 32), 0, s, a); break;
+    default: launch(qkv_post_kernel<T, 8>, dim3((int)blocks), dim3(warps * 32), 0, s, a); break;
   }
   return check_launch("qkv_post");
 }

@@ -36,6 +36,7 @@ __device__ __forceinline__ unsigned long long mass_of(float x, float mx) {
 __global__ void penalize_kernel(float* logits, long long ld, int limit, const int* recent, const int* n_recent,
                                 int recent_stride, float penalty, const int* banned, const int* n_banned,
                                 int banned_stride) {
+  pdl_enter();
   const int r = blockIdx.x;
   float* row = logits + (size_t)r * ld;
   if (banned) {
@@ -67,6 +68,7 @@ constexpr int kArgmaxThreads = 256;
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_partial_kernel(const float* __restrict__ logits, long long ld, int limit, float* __restrict__ part_v,
                       int* __restrict__ part_i) {
+  pdl_enter();
   __shared__ float best_v[8];
   __shared__ int best_i[8];
   const int r = blockIdx.y, chunk = blockIdx.x;
@@ -101,6 +103,7 @@ argmax_partial_kernel(const float* __restrict__ logits, long long ld, int limit,
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int* __restrict__ out) {
+  pdl_enter();
   const int r = blockIdx.x, lane = threadIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -180,6 +183,7 @@ __device__ unsigned int radix_threshold(const float* row, int limit, float temp,
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, long long ld, int limit, float temperature, int top_k, float top_p,
               float min_p, const float* __restrict__ uniform, int* __restrict__ out) {
+  pdl_enter();
   __shared__ SampleShared sh;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
@@ -271,7 +275,7 @@ extern "C" int slb_penalize(float* logits, long long ld, int rows, int limit, co
   SLB_REQUIRE(rows >= 0 && limit > 0 && ld >= limit, "penalize: rows=%d limit=%d ld=%lld", rows, limit, ld);
   SLB_REQUIRE(penalty > 0.0f, "penalize: repetition penalty must be positive, got %g", (double)penalty);
   if (rows == 0 || (!recent && !banned)) return 0;
-  penalize_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(logits, ld, limit, recent, n_recent, recent_stride, penalty,
+  launch(penalize_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, logits, ld, limit, recent, n_recent, recent_stride, penalty,
                                                           banned, n_banned, banned_stride);
   return check_launch("penalize");
 }
@@ -288,10 +292,10 @@ extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit
   float* part_v = (float*)scratch;
   int* part_i = (int*)scratch + (size_t)rows * kArgmaxChunks;
   cudaStream_t s = (cudaStream_t)stream;
-  argmax_partial_kernel<<<dim3(kArgmaxChunks, rows), kArgmaxThreads, 0, s>>>(logits, ld, limit, part_v, part_i);
+  launch(argmax_partial_kernel, dim3(dim3(kArgmaxChunks, rows)), dim3(kArgmaxThreads), 0, s, logits, ld, limit, part_v, part_i);
   int rc = check_launch("argmax (slices)");
   if (rc) return rc;
-  argmax_final_kernel<<<rows, 32, 0, s>>>(part_v, part_i, out);
+  launch(argmax_final_kernel, dim3(rows), dim3(32), 0, s, part_v, part_i, out);
   return check_launch("argmax");
 }
 
@@ -303,7 +307,7 @@ extern "C" int slb_sample(const float* logits, long long ld, int rows, int limit
   SLB_REQUIRE(top_k >= 0 && top_p > 0.0f && min_p >= 0.0f && min_p <= 1.0f, "sample: top_k=%d top_p=%g min_p=%g", top_k,
               (double)top_p, (double)min_p);
   if (rows == 0) return 0;
-  sample_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, ld, limit, temperature, top_k, top_p, min_p,
+  launch(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, (cudaStream_t)stream, logits, ld, limit, temperature, top_k, top_p, min_p,
                                                                   uniform, out);
   return check_launch("sample");
 }
