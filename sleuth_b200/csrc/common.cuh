@@ -39,12 +39,13 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_wait();
 }
 
-bool pdl_enabled();
+int pdl_mode();                       // 0 off, 1 every kernel, 2 only kernels that prefetch before their wait
+inline bool pdl_enabled() { return pdl_mode() != 0; }
 void note_launch_error(cudaError_t e);
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                          Args... args) {
+inline cudaError_t launch_with(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -52,12 +53,24 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = early ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
   if (e != cudaSuccess) note_launch_error(e);
   return e;
+}
+
+// Ordinary kernels: allowed to start early only in mode 1. Kernels that fetch weights before their wait: modes 1 and 2.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  return launch_with(pdl_mode() == 1, kernel, grid, block, smem, stream, args...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_prefetching(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args... args) {
+  return launch_with(pdl_mode() != 0, kernel, grid, block, smem, stream, args...);
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

@@ -19,12 +19,12 @@ int fail(int code, const char* fmt, ...) {
 
 static int g_pdl = -1;
 
-bool pdl_enabled() {
+int pdl_mode() {
   if (g_pdl < 0) {
     const char* e = getenv("SLEUTH_B200_PDL");
-    g_pdl = (e && e[0] == '0') ? 0 : 1;
+    g_pdl = e ? (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1)) : 0;
   }
-  return g_pdl == 1;
+  return g_pdl;
 }
 
 static thread_local cudaError_t g_launch_error = cudaSuccess;
@@ -46,5 +46,5 @@ extern "C" const char* slb_last_error() { return slb::g_message; }
 extern "C" int slb_abi_version() { return 1; }
 
 // 1: kernels may start while their predecessor still runs (programmatic dependent launch); 0: strictly one after another.
-extern "C" void slb_set_pdl(int on) { slb::g_pdl = on ? 1 : 0; }
-extern "C" int slb_get_pdl() { return slb::pdl_enabled() ? 1 : 0; }
+extern "C" void slb_set_pdl(int mode) { slb::g_pdl = mode < 0 || mode > 2 ? 0 : mode; }
+extern "C" int slb_get_pdl() { return slb::pdl_mode(); }

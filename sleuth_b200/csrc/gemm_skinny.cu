@@ -24,6 +24,9 @@ namespace slb {
 enum SkinnyMode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwiglu = 3 };
 
 struct SkinnyArgs {
+  const float* Xf;          // NORM: the float32 stream [M, K]; rows are normalised on the fly
+  const float* gain;        // NORM: [K]
+  float eps;
   const __nv_bfloat16* X;   // [M, K]
   const __nv_bfloat16* W;   // [N, K]  (kSwiglu: [2 * inter, K], gate rows then up rows)
   void* C;                  // [M, ldc]
@@ -44,13 +47,23 @@ __device__ __forceinline__ uint4 ldg16(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 constexpr int kSkinnyWarps = 8;
 constexpr int kUnroll = 4;       // blocks of 32 k values fetched before any is used
 
-template <int NF, int MODE>
+// NORM: X is not given; instead the block normalises the rows of the float32 stream itself,
+// h = (x * 1/sqrt(mean(x^2) + eps)) * gain rounded to bfloat16 (sleuth/forge/model/norm.py:50), which saves the
+// separate norm kernel and the round trip of h through memory. Every block recomputes the row sums (M * K floats
+// from L2), after its weight loads have gone out.
+template <int NF, int MODE, bool NORM>
 __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   __shared__ float red[kSkinnyWarps][TILES][16][8 + 1];
+  __shared__ float inv_rms[16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NF * 8);
@@ -66,8 +79,10 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
     const int row = (MODE == kSwiglu && f >= NF) ? a.N + feat : feat;
     wrow[f] = feat < a.N ? a.W + (size_t)row * a.K + 8 * t : nullptr;
   }
-  const __nv_bfloat16* xrow0 = g < a.M ? a.X + (size_t)g * a.K + 8 * t : nullptr;
-  const __nv_bfloat16* xrow1 = g + 8 < a.M ? a.X + (size_t)(g + 8) * a.K + 8 * t : nullptr;
+  const __nv_bfloat16* xrow0 = (!NORM && g < a.M) ? a.X + (size_t)g * a.K + 8 * t : nullptr;
+  const __nv_bfloat16* xrow1 = (!NORM && g + 8 < a.M) ? a.X + (size_t)(g + 8) * a.K + 8 * t : nullptr;
+  const float* frow0 = (NORM && g < a.M) ? a.Xf + (size_t)g * a.K + 8 * t : nullptr;
+  const float* frow1 = (NORM && g + 8 < a.M) ? a.Xf + (size_t)(g + 8) * a.K + 8 * t : nullptr;
 
   float acc[TILES][4];
 #pragma unroll
@@ -89,6 +104,37 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
   pdl_launch_dependents();
   fetch_weights(kb_begin);
   pdl_wait();
+  float inv0 = 0.0f, inv1 = 0.0f;
+  if (NORM) {
+    // sum of squares of every row: thread i adds the float4 chunks i, i + 256, ... of each row, the 32 lanes and
+    // then the 8 warps are added in a fixed order
+    float* part = &red[0][0][0][0];                 // [8 warps][16 rows], reused before the product needs it
+    const int n4 = a.K >> 2;
+    for (int r = 0; r < a.M; ++r) {
+      const float4* xr = reinterpret_cast<const float4*>(a.Xf + (size_t)r * a.K);
+      float ss = 0.0f;
+      for (int c = threadIdx.x; c < n4; c += kSkinnyWarps * 32) {
+        const float4 v = xr[c];
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) part[warp * 16 + r] = ss;
+    }
+    __syncthreads();
+    if (threadIdx.x < a.M) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int w8 = 0; w8 < kSkinnyWarps; ++w8) ss += part[w8 * 16 + threadIdx.x];
+      inv_rms[threadIdx.x] = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+    }
+    __syncthreads();
+    inv0 = g < a.M ? inv_rms[g] : 0.0f;
+    inv1 = g + 8 < a.M ? inv_rms[g + 8] : 0.0f;
+    __syncthreads();                                // `red` is written again only after everyone has read `part`
+  }
   for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
     if (kb != kb_begin) fetch_weights(kb);
     uint4 x0[kUnroll], x1[kUnroll];
@@ -96,8 +142,31 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
     for (int u = 0; u < kUnroll; ++u) {
       const bool live = kb + u < kb_end;
       const int off = (kb + u) * 32;
-      x0[u] = (live && xrow0) ? *reinterpret_cast<const uint4*>(xrow0 + off) : zero;
-      x1[u] = (live && xrow1) ? *reinterpret_cast<const uint4*>(xrow1 + off) : zero;
+      if (NORM) {
+        x0[u] = zero;
+        x1[u] = zero;
+        if (live) {
+          const float4 g0 = *reinterpret_cast<const float4*>(a.gain + off + 8 * t);
+          const float4 g1 = *reinterpret_cast<const float4*>(a.gain + off + 8 * t + 4);
+          if (frow0) {
+            const float4 p = *reinterpret_cast<const float4*>(frow0 + off), q = *reinterpret_cast<const float4*>(frow0 + off + 4);
+            x0[u].x = pack2((p.x * inv0) * g0.x, (p.y * inv0) * g0.y);
+            x0[u].y = pack2((p.z * inv0) * g0.z, (p.w * inv0) * g0.w);
+            x0[u].z = pack2((q.x * inv0) * g1.x, (q.y * inv0) * g1.y);
+            x0[u].w = pack2((q.z * inv0) * g1.z, (q.w * inv0) * g1.w);
+          }
+          if (frow1) {
+            const float4 p = *reinterpret_cast<const float4*>(frow1 + off), q = *reinterpret_cast<const float4*>(frow1 + off + 4);
+            x1[u].x = pack2((p.x * inv1) * g0.x, (p.y * inv1) * g0.y);
+            x1[u].y = pack2((p.z * inv1) * g0.z, (p.w * inv1) * g0.w);
+            x1[u].z = pack2((q.x * inv1) * g1.x, (q.y * inv1) * g1.y);
+            x1[u].w = pack2((q.z * inv1) * g1.z, (q.w * inv1) * g1.w);
+          }
+        }
+      } else {
+        x0[u] = (live && xrow0) ? *reinterpret_cast<const uint4*>(xrow0 + off) : zero;
+        x1[u] = (live && xrow1) ? *reinterpret_cast<const uint4*>(xrow1 + off) : zero;
+      }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -143,17 +212,26 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
   }
 }
 
-template <int NF>
+template <int NF, bool NORM>
 static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
   const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
   const int threads = kSkinnyWarps * 32;
   switch (mode) {
-    case kStoreBf16: launch(gemm_skinny_kernel<NF, kStoreBf16>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kStoreF32: launch(gemm_skinny_kernel<NF, kStoreF32>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kAddF32: launch(gemm_skinny_kernel<NF, kAddF32>, dim3(blocks), dim3(threads), 0, s, a); break;
-    default: launch(gemm_skinny_kernel<NF, kSwiglu>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreBf16: launch_prefetching(gemm_skinny_kernel<NF, kStoreBf16, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreF32: launch_prefetching(gemm_skinny_kernel<NF, kStoreF32, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kAddF32: launch_prefetching(gemm_skinny_kernel<NF, kAddF32, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
+    default: launch_prefetching(gemm_skinny_kernel<NF, kSwiglu, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
   }
   return check_launch("gemm_skinny");
+}
+
+template <bool NORM>
+static int dispatch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
+  // wide matrices: 16 or 32 features per block; narrow ones: 8, so that enough blocks exist to fill the GPU
+  if (mode == kSwiglu) return a.N >= 4096 ? launch_skinny<2, NORM>(a, mode, s) : launch_skinny<1, NORM>(a, mode, s);
+  if (a.N >= 32768) return launch_skinny<4, NORM>(a, mode, s);
+  if (a.N >= 4096) return launch_skinny<2, NORM>(a, mode, s);
+  return launch_skinny<1, NORM>(a, mode, s);
 }
 
 }  // namespace slb
@@ -172,12 +250,21 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: X and W must be 16-byte aligned");
-  SkinnyArgs a;
+  SkinnyArgs a{};
   a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
-  cudaStream_t s = (cudaStream_t)stream;
-  // wide matrices: 16 or 32 features per block; narrow ones: 8, so that enough blocks exist to fill the GPU
-  if (mode == kSwiglu) return N >= 4096 ? launch_skinny<2>(a, mode, s) : launch_skinny<1>(a, mode, s);
-  if (N >= 32768) return launch_skinny<4>(a, mode, s);
-  if (N >= 4096) return launch_skinny<2>(a, mode, s);
-  return launch_skinny<1>(a, mode, s);
+  return dispatch_skinny<false>(a, mode, (cudaStream_t)stream);
+}
+
+// The same with the RMSNorm of the input fused in: X is the float32 stream [M, K], rows are normalised with
+// `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
+extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
+                                    int K, int ldc, int mode, void* stream) {
+  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
+              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
+  SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N && eps > 0.0f, "gemm_skinny: mode=%d ldc=%d N=%d eps=%g", mode, ldc, N, (double)eps);
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)gain % 16 == 0),
+              "gemm_skinny: X, gain and W must be 16-byte aligned");
+  SkinnyArgs a{};
+  a.Xf = X; a.gain = gain; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  return dispatch_skinny<true>(a, mode, (cudaStream_t)stream);
 }

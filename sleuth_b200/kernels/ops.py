@@ -196,6 +196,20 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, 
                stream if stream is not None else current_stream())
 
 
+def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor, mode: str,
+                     stream=None) -> None:
+    """``gemm_skinny`` on rmsnorm(x; gain, eps): x is the float32 stream [M, K], normalised inside the kernel."""
+    _cuda(x, gain, w, out)
+    M, K = x.shape
+    N = out.shape[1]
+    _need(x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == K, "gemm_skinny_norm: x and gain are float32")
+    _need(w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape[0] == M, "gemm_skinny_norm: shapes or dtypes")
+    _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny_norm: weight rows")
+    _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny_norm: output dtype")
+    lib().call("slb_gemm_skinny_norm", _p(x), _p(gain), float(eps), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode],
+               stream if stream is not None else current_stream())
+
+
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:
     _cuda(logits, recent, n_recent, banned, n_banned)
     R = logits.shape[0]

@@ -25,6 +25,8 @@ from .spec import AttentionSpec
 
 
 class GQAAttention(Part):
+    accepts_normed = True
+
     def __init__(self, spec: AttentionSpec, ctx: BuildContext):
         if spec.heads % spec.kv_heads:
             raise ValueError(f"heads ({spec.heads}) must be a multiple of kv_heads ({spec.kv_heads})")

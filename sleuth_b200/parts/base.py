@@ -15,6 +15,7 @@ is float32 ``[tokens, hidden]``; ``h`` is in the run dtype):
 * position:  ``tables() -> (cos, sin) | None``                 what the attention kernels read
 * mixer:     ``forward(h, x, b, view, ws)``                    adds its output into ``x`` in place
 * ffn:       ``forward(h, x, b, ws)``                          adds its output into ``x`` in place
+             (a mixer or ffn with ``accepts_normed = True`` gets a ``Normed`` for ``h``, see below)
 * layer:     ``forward(x, b, view, ws)``                       one whole layer on the stream, in place
 * embedding: ``forward(ids, x)``                               fills ``x`` from token ids
 * head:      ``forward(x, rows, logits, ws)``                  final norm + output matrix on chosen rows
@@ -51,7 +52,30 @@ class BuildContext:
     shared: dict = field(default_factory=dict)   # parts that several layers share (position tables)
 
 
+class Normed:
+    """The normalised rows of the stream, handed to a mixer or feed-forward that set ``accepts_normed``.
+
+    Such a part may either ask for the tensor (``tensor()`` runs the norm kernel once and keeps the result)
+    or, when its first product can normalise on the fly, read ``x``, ``gain`` and ``eps`` and skip the
+    norm kernel altogether. ``gain`` is None when the norm is not a plain RMSNorm."""
+
+    def __init__(self, norm, x: torch.Tensor, ws, stream, dtype):
+        self.norm, self.x, self.ws, self.stream, self.dtype = norm, x, ws, stream, dtype
+        self.gain = getattr(norm, "weight", None) if getattr(norm, "fusable", False) else None
+        self.eps = getattr(norm, "eps", 0.0)
+        self.shape = x.shape
+        self._h = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._h is None:
+            self._h = self.ws.take(self.x.shape, self.dtype)
+            self.norm.forward(self.x, self._h, stream=self.stream)
+        return self._h
+
+
 class Part:
+    accepts_normed = False      # True: ``forward`` takes a ``Normed`` instead of the normalised tensor
+
     def declare(self) -> dict[str, ParamDecl]:
         return {}
 

@@ -7,12 +7,14 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, ParamDecl, Part, register_ffn
+from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
 from .linear import Linear
 from .spec import GatedMLPSpec
 
 
 class GatedMLP(Part):
+    accepts_normed = True
+
     def __init__(self, spec: GatedMLPSpec, ctx: BuildContext):
         if spec.activation != "silu":
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported (silu)")
@@ -33,7 +35,11 @@ class GatedMLP(Part):
         mark = ws.mark()
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
         if self.ctx.dtype == torch.bfloat16 and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden):
-            ops.gemm_skinny(h, self.gate_up.weight, act, "swiglu", b.stream)      # activation in the product's epilogue
+            # norm in the product's prologue (when handed the stream), activation in its epilogue
+            if isinstance(h, Normed) and h.gain is not None:
+                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream)
+            else:
+                ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
             ops.swiglu(gu, act, b.stream)

@@ -7,7 +7,7 @@ itself is a float32 accumulation into the stream, done by the last product of th
 
 from __future__ import annotations
 
-from .base import BuildContext, Part, build_ffn, build_mixer, build_norm, register_layer
+from .base import BuildContext, Normed, Part, build_ffn, build_mixer, build_norm, register_layer
 from .spec import LayerSpec
 
 
@@ -36,12 +36,16 @@ class PreNormLayer(Part):
 
     def forward(self, x, b, view, ws):
         mark = ws.mark()
-        h = ws.take(x.shape, self.ctx.dtype)
-        self.norm1.forward(x, h, stream=b.stream)
-        self.mixer.forward(h, x, b, view, ws)
-        self.norm2.forward(x, h, stream=b.stream)
-        self.ffn.forward(h, x, b, ws)
+        self.mixer.forward(self._input(self.norm1, self.mixer, x, b, ws), x, b, view, ws)
         ws.release(mark)
+        self.ffn.forward(self._input(self.norm2, self.ffn, x, b, ws), x, b, ws)
+        ws.release(mark)
+
+    def _input(self, norm, part, x, b, ws):
+        """What ``part`` reads: the normalised tensor, or, for a part that can normalise inside its first
+        product, a ``Normed`` that runs the norm kernel only if asked for the tensor."""
+        n = Normed(norm, x, ws, b.stream, self.ctx.dtype)
+        return n if part.accepts_normed else n.tensor()
 
 
 register_layer("prenorm", PreNormLayer)

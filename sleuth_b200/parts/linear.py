@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .base import Normed
 
 
 _MODE: dict = {}
@@ -56,6 +57,16 @@ class Linear:
     def forward(self, h: torch.Tensor, out: torch.Tensor | None = None, into: torch.Tensor | None = None,
                 ws=None, stream=None, out_dtype: torch.dtype | None = None):
         M = h.shape[0]
+        if isinstance(h, Normed):
+            if (self.dtype == torch.bfloat16 and h.gain is not None and into is None
+                    and ops.skinny_supported(M, self.out_features, self.in_features)):
+                want = out_dtype or (out.dtype if out is not None else self.dtype)
+                if out is None:
+                    out = ws.take((M, self.out_features), want)
+                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, "f32" if want == torch.float32 else "bf16",
+                                     stream)
+                return out
+            h = h.tensor()
         if self.dtype == torch.float32:
             if into is not None:
                 ops.gemm_f32(h, self.weight, into, accumulate=True, stream=stream)

@@ -11,6 +11,8 @@ from .spec import NormSpec
 
 
 class RMSNorm(Part):
+    fusable = True      # a product kernel may apply this norm itself from ``weight`` and ``eps``
+
     def __init__(self, spec: NormSpec, ctx: BuildContext):
         self.dim, self.eps, self.dtype = spec.dim, spec.eps, ctx.dtype
         self.weight = None

@@ -327,3 +327,28 @@ def test_argmax_first_index_on_ties(rows, vocab, limit):
     o.argmax(logits.to(DEV), limit, out, scratch)
     want = [int(torch.nonzero(r[:limit] == r[:limit].max())[0]) for r in logits]
     assert out.cpu().tolist() == want
+
+
+@pytest.mark.parametrize("M,N,K,mode", [(1, 4096, 1024, "bf16"), (8, 1024, 2048, "f32"), (16, 200, 96, "bf16"),
+                                         (5, 3072, 1024, "swiglu"), (3, 136, 64, "swiglu")])
+def test_gemm_skinny_with_the_norm_fused_in(M, N, K, mode):
+    """The product that normalises its input rows itself equals norm kernel + product, up to the rounding of h."""
+    o = ops()
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(M, K, generator=g) * 2
+    gain = 1 + 0.2 * torch.randn(K, generator=g)
+    eps = 1e-5
+    rows = 2 * N if mode == "swiglu" else N
+    w = (torch.randn(rows, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    h = (x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * gain.double())
+    hb = h.to(torch.bfloat16).double()          # the kernel rounds h to bfloat16 before the product
+    if mode == "swiglu":
+        a, b = hb @ w[:N].double().T, hb @ w[N:].double().T
+        ref = a * torch.sigmoid(a) * b
+    else:
+        ref = hb @ w.double().T
+    dt = torch.float32 if mode == "f32" else torch.bfloat16
+    out = torch.full((M, N), float("nan"), dtype=dt, device=DEV)
+    o.gemm_skinny_norm(x.to(DEV), gain.to(DEV), eps, w.to(DEV), out, mode)
+    tl = dict(rtol=2e-2, atol=2e-2) if dt == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(out.cpu().double(), ref, **tl)
