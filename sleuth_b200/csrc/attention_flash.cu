@@ -16,8 +16,8 @@
 //   * attn_decode_kernel: every sequence brings one token, so a (sequence, kv head) has only G rows. A block
 //     takes one slice of the sequence's pages (split-KV); its 4 warps take 16 keys each of every page, and
 //     their partial results (max, sum, weighted values) are merged through shared memory. With more than one
-//     slice the block writes an unnormalised partial result to scratch memory and attn_combine_kernel merges
-//     the slices.
+//     slice the block writes an unnormalised partial result to scratch memory, and the block that finishes last
+//     (a ticket counter per sequence and kv head tells which) merges the slices in slice order.
 // Shared-memory tiles are [64 rows][HD] bfloat16 with the 16-byte chunks of a row XOR-swizzled by the row
 // number, which keeps ldmatrix free of bank conflicts.
 #include <math.h>
@@ -42,6 +42,7 @@ struct FlashArgs {
   int splits;
   float* part_o;                // [n, H, splits, HD] unnormalised
   float* part_ml;               // [n, H, splits, 2]  running max (log2 units) and sum
+  int* counters;                // [n, kv_heads, row_tiles] zero between launches: slices that have finished
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -306,6 +307,12 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   const int* table = a.block_table + (size_t)seq * a.table_stride;
   const int head0 = kh * G + rt * 16;          // first query head of this row tile
   const int rows = min(16, G - rt * 16);
+  // this slice's page numbers, fetched once so that the page loop does not wait for the table
+  __shared__ int my_pages[kFlashThreads];
+  __shared__ int ticket;
+  if (my_lo + tid <= my_hi) my_pages[tid] = table[my_lo + tid];
+  auto page_of = [&](int page) { return page - my_lo < kFlashThreads ? my_pages[page - my_lo] : table[page]; };
+  __syncthreads();
 
   float o[HD / 8][4];
 #pragma unroll
@@ -321,7 +328,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
         *reinterpret_cast<uint4*>(sQ_ptr + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
     }
     {
-      const size_t base = ((size_t)table[my_lo] * a.kv_heads + kh) * 64 * HD;
+      const size_t base = ((size_t)page_of(my_lo) * a.kv_heads + kh) * 64 * HD;
       load_page<HD, kFlashThreads>(smem, 0, a.k_pool + base, pos + 1 - my_lo * 64, tid);
       load_page<HD, kFlashThreads>(smem, 2 * TILE, a.v_pool + base, pos + 1 - my_lo * 64, tid);
     }
@@ -338,7 +345,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     for (int page = my_lo; page <= my_hi; ++page) {
       const int stage = (page - my_lo) & 1;
       if (page < my_hi) {
-        const size_t base = ((size_t)table[page + 1] * a.kv_heads + kh) * 64 * HD;
+        const size_t base = ((size_t)page_of(page + 1) * a.kv_heads + kh) * 64 * HD;
         load_page<HD, kFlashThreads>(smem, (stage ^ 1) * TILE, a.k_pool + base, pos + 1 - (page + 1) * 64, tid);
         load_page<HD, kFlashThreads>(smem, (2 + (stage ^ 1)) * TILE, a.v_pool + base, pos + 1 - (page + 1) * 64, tid);
         cp_async_commit();
@@ -459,25 +466,34 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       if (d == 0) { a.part_ml[pi * 2] = m; a.part_ml[pi * 2 + 1] = l; }
     }
   }
-}
+  if (a.splits == 1) return;
 
-// grid: (sequences * heads); block: HD threads. Merges the slices of attn_decode_kernel.
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_start, int heads,
-                                    int splits, int hd) {
-  pdl_enter();
-  const int seq = blockIdx.x / heads, head = blockIdx.x % heads, d = threadIdx.x;
-  const size_t base = ((size_t)seq * heads + head) * splits;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-  const float m_use = m == -INFINITY ? 0.0f : m;
-  float l = 0.0f, acc = 0.0f;
-  for (int s = 0; s < splits; ++s) {
-    const float f = exp2f(part_ml[(base + s) * 2] - m_use);
-    l += part_ml[(base + s) * 2 + 1] * f;
-    acc += part_o[(base + s) * hd + d] * f;
+  // The slice that finishes last merges all slices of its (sequence, kv head, row tile): every block publishes
+  // its partial result, then takes a ticket; the holder of the last ticket reads them all back, always in slice
+  // order, so the sum does not depend on which block that is. It leaves the counter at zero for the next launch.
+  __threadfence();
+  __syncthreads();
+  int* counter = a.counters + ((size_t)seq * a.kv_heads + kh) * row_tiles + rt;
+  if (tid == 0) ticket = atomicAdd(counter, 1);
+  __syncthreads();
+  if (ticket != a.splits - 1) return;
+  __threadfence();
+  for (int idx = tid; idx < rows * HD; idx += kFlashThreads) {
+    const int row = idx / HD, d = idx % HD;
+    const int head = head0 + row;
+    const size_t base = ((size_t)seq * a.heads + head) * a.splits;
+    float m = -INFINITY;
+    for (int s2 = 0; s2 < a.splits; ++s2) m = fmaxf(m, __ldcg(a.part_ml + (base + s2) * 2));
+    const float m_use = m == -INFINITY ? 0.0f : m;
+    float l = 0.0f, acc = 0.0f;
+    for (int s2 = 0; s2 < a.splits; ++s2) {
+      const float f = exp2f(__ldcg(a.part_ml + (base + s2) * 2) - m_use);
+      l += __ldcg(a.part_ml + (base + s2) * 2 + 1) * f;
+      acc += __ldcg(a.part_o + (base + s2) * HD + d) * f;
+    }
+    a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
   }
-  out[((size_t)seq_start[seq] * heads + head) * hd + d] = __float2bfloat16_rn(acc / l);
+  if (tid == 0) *counter = 0;
 }
 
 template <int HD>
@@ -511,10 +527,7 @@ static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
   }
   dim3 grid(a.splits * row_tiles, a.kv_heads, n_seqs);
   launch(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
-  int rc = check_launch("attention (decode)");
-  if (rc || a.splits == 1) return rc;
-  launch(attn_combine_kernel, dim3(n_seqs * a.heads), dim3(HD), 0, s, a.part_o, a.part_ml, a.out, a.seq_start, a.heads, a.splits, HD);
-  return check_launch("attention (combine)");
+  return check_launch("attention (decode)");
 }
 
 }  // namespace slb
@@ -552,7 +565,8 @@ extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const vo
 extern "C" int slb_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
                                     const int* seq_start, const int* past, const int* block_table, int table_stride,
                                     int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
-                                    int splits, float* scratch, long long scratch_floats, void* stream) {
+                                    int splits, float* scratch, long long scratch_floats, int* counters,
+                                    long long n_counters, void* stream) {
   SLB_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention (decode): seqs=%d heads=%d kv_heads=%d", n_seqs, heads, kv_heads);
   SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (decode): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
@@ -561,8 +575,11 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   const long long need = slb_attention_decode_scratch_floats(n_seqs, heads, head_dim, splits);
   SLB_REQUIRE(need == 0 || (scratch != nullptr && scratch_floats >= need),
               "attention (decode): %d slices need %lld floats of scratch memory, %lld were given", splits, need, scratch_floats);
+  SLB_REQUIRE(splits == 1 || (counters != nullptr && n_counters >= (long long)n_seqs * kv_heads * ((heads / kv_heads + 15) / 16)),
+              "attention (decode): %d slices need a zeroed counter per (sequence, kv head, row tile); %lld were given", splits, n_counters);
   if (n_seqs == 0) return 0;
   FlashArgs a{};
+  a.counters = counters;
   a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = nullptr;
   a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;

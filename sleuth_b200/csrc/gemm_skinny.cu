@@ -53,17 +53,21 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 constexpr int kSkinnyWarps = 8;
-constexpr int kUnroll = 4;       // blocks of 32 k values fetched before any is used
+// Blocks of 32 k values whose weights a warp fetches before it uses any: 8 sixteen-byte loads per lane in flight.
+__host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 : (tiles >= 4 ? 2 : (tiles >= 2 ? 4 : 8)); }
 
-// NORM: X is not given; instead the block normalises the rows of the float32 stream itself,
-// h = (x * 1/sqrt(mean(x^2) + eps)) * gain rounded to bfloat16 (sleuth/forge/model/norm.py:50), which saves the
-// separate norm kernel and the round trip of h through memory. Every block recomputes the row sums (M * K floats
-// from L2), after its weight loads have gone out.
+// NORM: X is not given; instead the block reads the float32 stream and applies the RMSNorm itself,
+// y = rmsnorm(x) W^T with rmsnorm(x) = x * gain / sqrt(mean(x^2) + eps) (sleuth/forge/model/norm.py:50). The row
+// factor 1/sqrt(..) is a scalar per row, so it is taken out of the product: the tensor cores multiply
+// bfloat16(x * gain) and the factor is applied to the float32 sums in the epilogue. The sum of squares is
+// gathered from the same loads that feed the product, so the norm costs no extra pass, no extra kernel and no
+// wait in front of the product.
 template <int NF, int MODE, bool NORM>
-__global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(kSkinnyWarps * 32, 2) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
+  constexpr int kUnroll = unroll_for(TILES);
   __shared__ float red[kSkinnyWarps][TILES][16][8 + 1];
-  __shared__ float inv_rms[16];
+  __shared__ float ssq_part[kSkinnyWarps][16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NF * 8);
@@ -104,37 +108,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
   pdl_launch_dependents();
   fetch_weights(kb_begin);
   pdl_wait();
-  float inv0 = 0.0f, inv1 = 0.0f;
-  if (NORM) {
-    // sum of squares of every row: thread i adds the float4 chunks i, i + 256, ... of each row, the 32 lanes and
-    // then the 8 warps are added in a fixed order
-    float* part = &red[0][0][0][0];                 // [8 warps][16 rows], reused before the product needs it
-    const int n4 = a.K >> 2;
-    for (int r = 0; r < a.M; ++r) {
-      const float4* xr = reinterpret_cast<const float4*>(a.Xf + (size_t)r * a.K);
-      float ss = 0.0f;
-      for (int c = threadIdx.x; c < n4; c += kSkinnyWarps * 32) {
-        const float4 v = xr[c];
-        ss = fmaf(v.x, v.x, ss);
-        ss = fmaf(v.y, v.y, ss);
-        ss = fmaf(v.z, v.z, ss);
-        ss = fmaf(v.w, v.w, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) part[warp * 16 + r] = ss;
-    }
-    __syncthreads();
-    if (threadIdx.x < a.M) {
-      float ss = 0.0f;
-#pragma unroll
-      for (int w8 = 0; w8 < kSkinnyWarps; ++w8) ss += part[w8 * 16 + threadIdx.x];
-      inv_rms[threadIdx.x] = 1.0f / sqrtf(ss / (float)a.K + a.eps);
-    }
-    __syncthreads();
-    inv0 = g < a.M ? inv_rms[g] : 0.0f;
-    inv1 = g + 8 < a.M ? inv_rms[g + 8] : 0.0f;
-    __syncthreads();                                // `red` is written again only after everyone has read `part`
-  }
+  float ssq0 = 0.0f, ssq1 = 0.0f;     // NORM: sums of squares of this lane's share of rows g and g + 8
   for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
     if (kb != kb_begin) fetch_weights(kb);
     uint4 x0[kUnroll], x1[kUnroll];
@@ -150,17 +124,19 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
           const float4 g1 = *reinterpret_cast<const float4*>(a.gain + off + 8 * t + 4);
           if (frow0) {
             const float4 p = *reinterpret_cast<const float4*>(frow0 + off), q = *reinterpret_cast<const float4*>(frow0 + off + 4);
-            x0[u].x = pack2((p.x * inv0) * g0.x, (p.y * inv0) * g0.y);
-            x0[u].y = pack2((p.z * inv0) * g0.z, (p.w * inv0) * g0.w);
-            x0[u].z = pack2((q.x * inv0) * g1.x, (q.y * inv0) * g1.y);
-            x0[u].w = pack2((q.z * inv0) * g1.z, (q.w * inv0) * g1.w);
+            ssq0 += (p.x * p.x + p.y * p.y) + (p.z * p.z + p.w * p.w) + (q.x * q.x + q.y * q.y) + (q.z * q.z + q.w * q.w);
+            x0[u].x = pack2(p.x * g0.x, p.y * g0.y);
+            x0[u].y = pack2(p.z * g0.z, p.w * g0.w);
+            x0[u].z = pack2(q.x * g1.x, q.y * g1.y);
+            x0[u].w = pack2(q.z * g1.z, q.w * g1.w);
           }
           if (frow1) {
             const float4 p = *reinterpret_cast<const float4*>(frow1 + off), q = *reinterpret_cast<const float4*>(frow1 + off + 4);
-            x1[u].x = pack2((p.x * inv1) * g0.x, (p.y * inv1) * g0.y);
-            x1[u].y = pack2((p.z * inv1) * g0.z, (p.w * inv1) * g0.w);
-            x1[u].z = pack2((q.x * inv1) * g1.x, (q.y * inv1) * g1.y);
-            x1[u].w = pack2((q.z * inv1) * g1.z, (q.w * inv1) * g1.w);
+            ssq1 += (p.x * p.x + p.y * p.y) + (p.z * p.z + p.w * p.w) + (q.x * q.x + q.y * q.y) + (q.z * q.z + q.w * q.w);
+            x1[u].x = pack2(p.x * g0.x, p.y * g0.y);
+            x1[u].y = pack2(p.z * g0.z, p.w * g0.w);
+            x1[u].z = pack2(q.x * g1.x, q.y * g1.y);
+            x1[u].w = pack2(q.z * g1.z, q.w * g1.w);
           }
         }
       } else {
@@ -186,6 +162,15 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
     red[warp][f][g + 8][2 * t] = acc[f][2];
     red[warp][f][g + 8][2 * t + 1] = acc[f][3];
   }
+  if (NORM) {
+    // the eight warps' slices of K cover every element of rows 0..15 exactly once, so the row sums of squares
+    // come from the very loads that fed the product: lanes of a quad, then warps, added in a fixed order
+    ssq0 += __shfl_xor_sync(0xffffffffu, ssq0, 1);
+    ssq0 += __shfl_xor_sync(0xffffffffu, ssq0, 2);
+    ssq1 += __shfl_xor_sync(0xffffffffu, ssq1, 1);
+    ssq1 += __shfl_xor_sync(0xffffffffu, ssq1, 2);
+    if (t == 0) { ssq_part[warp][g] = ssq0; ssq_part[warp][g + 8] = ssq1; }
+  }
   __syncthreads();
 
   for (int idx = threadIdx.x; idx < 16 * NF * 8; idx += kSkinnyWarps * 32) {
@@ -196,10 +181,19 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(SkinnyAr
     float v = 0.0f;
 #pragma unroll
     for (int w8 = 0; w8 < kSkinnyWarps; ++w8) v += red[w8][f][r][cc];
+    float inv = 1.0f;
+    if (NORM) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int w8 = 0; w8 < kSkinnyWarps; ++w8) ss += ssq_part[w8][r];
+      inv = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+      v *= inv;
+    }
     if (MODE == kSwiglu) {
       float u = 0.0f;
 #pragma unroll
       for (int w8 = 0; w8 < kSkinnyWarps; ++w8) u += red[w8][NF + f][r][cc];
+      u *= inv;
       v = (v / (1.0f + expf(-v))) * u;
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
     } else if (MODE == kStoreBf16) {

@@ -135,7 +135,7 @@ _SIGNATURES = {
     "slb_qkv_post": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "slb_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "slb_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
-    "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P],
+    "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P],
     "slb_gemm_skinny": [P, P, P, I, I, I, I, I, P],
     "slb_gemm_skinny_norm": [P, P, F, P, P, I, I, I, I, I, P],
     "slb_gemm_f32": [P, P, P, P, I, I, I, I, I, I, I, P],
@@ -153,6 +153,7 @@ class KernelLibrary:
         self.dll = ctypes.CDLL(str(path))
         self.dll.slb_last_error.restype = ctypes.c_char_p
         self._fns = {}
+        self.timing = None
         self.launches = 0      # launcher calls made through ``call`` (each starts at least one kernel)
         for name, argtypes in _SIGNATURES.items():
             self.declare(name, argtypes)
@@ -164,8 +165,36 @@ class KernelLibrary:
         self._fns[name] = fn
 
     def call(self, name: str, *args) -> None:
+        if self.timing is not None:
+            return self._timed_call(name, *args)
         rc = self._fns[name](*args)
         self.launches += 1
+        if rc != 0:
+            raise RuntimeError(self.dll.slb_last_error().decode("utf-8", "replace"))
+
+    # ---- per-launcher device times, for finding where a step's time goes (off unless start_timing was called) ----
+    def start_timing(self) -> None:
+        self.timing = []
+
+    def stop_timing(self) -> dict:
+        """{launcher name: (calls, total milliseconds on the device)}; ends the timing mode."""
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.timing or []:
+            n, t = out.get(name, (0, 0.0))
+            out[name] = (n + 1, t + a.elapsed_time(b))
+        self.timing = None
+        return out
+
+    def _timed_call(self, name: str, *args) -> None:
+        import torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = self._fns[name](*args)
+        b.record()
+        self.launches += 1
+        self.timing.append((name, a, b))
         if rc != 0:
             raise RuntimeError(self.dll.slb_last_error().decode("utf-8", "replace"))
 

@@ -127,7 +127,12 @@ def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> 
     GPU a few times over, never more than a sequence can have pages. It depends on the batch size
     only, not on the lengths, so a captured step stays valid as sequences grow."""
     blocks = max(1, n_seqs * kv_heads * ((group + 15) // 16))
-    return max(1, min(-(-592 // blocks), 32, table_stride))
+    # three blocks of this kernel fit an SM (shared memory): 148 * 3 run at once. All slices should run in one
+    # wave, or else in whole waves.
+    resident = 148 * 3
+    if blocks >= resident:
+        return 1
+    return max(1, min(resident // blocks, 64, table_stride))
 
 
 def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
@@ -153,10 +158,29 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(scratch is None or scratch.dtype == torch.float32, "attention: scratch is float32")
+    counters = _decode_counters(q.device, n * kv_heads * ((heads // kv_heads + 15) // 16)) if splits > 1 else None
     lib().call("slb_attention_decode", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
                _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
-               int(splits), _p(scratch), 0 if scratch is None else scratch.numel(),
-               stream if stream is not None else current_stream())
+               int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
+               0 if counters is None else counters.numel(), stream if stream is not None else current_stream())
+
+
+_COUNTERS: dict = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Ticket counters of the split-KV decode kernel: zero when a launch starts, left at zero when it ends."""
+    key = str(device)
+    t = _COUNTERS.get(key)
+    if t is None or t.numel() < n:
+        if t is not None:
+            _RETIRED.append(t)          # a captured graph may still point at the smaller one
+        t = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+        _COUNTERS[key] = t
+    return t
+
+
+_RETIRED: list = []
 
 
 def decode_scratch_floats(n_seqs: int, heads: int, head_dim: int, splits: int) -> int:
