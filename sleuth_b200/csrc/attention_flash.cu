@@ -283,14 +283,19 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
 
 // ------------------------------------------------------------------------------------- decode ----
 // grid: (splits * row_tiles, kv_heads, sequences); every sequence has count 1.
+// Three page buffers: while one page is being multiplied, the next two are already on their way, which is what
+// keeps the memory system busy when a block's work per page is short compared with the latency of a load.
+constexpr int kDecodeStages = 3;
+
 template <int HD>
 __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
   pdl_enter();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;
-  const uint32_t sK = smem_u32(smem), sV = sK + 2 * TILE;
-  const uint32_t sQ = sV + 2 * TILE;          // [16][HD]
-  unsigned char* sQ_ptr = smem + 4 * TILE;
+  constexpr int S = kDecodeStages;
+  const uint32_t sK = smem_u32(smem), sV = sK + S * TILE;
+  const uint32_t sQ = sV + S * TILE;          // [16][HD]
+  unsigned char* sQ_ptr = smem + 2 * S * TILE;
 
   const int seq = blockIdx.z, kh = blockIdx.y;
   const int G = a.heads / a.kv_heads;
@@ -320,6 +325,15 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
 
   if (my_lo <= my_hi) {
+    auto fetch = [&](int page) {      // one commit group per page, empty beyond the slice
+      if (page <= my_hi) {
+        const int st = (page - my_lo) % S;
+        const size_t base = ((size_t)page_of(page) * a.kv_heads + kh) * 64 * HD;
+        load_page<HD, kFlashThreads>(smem, st * TILE, a.k_pool + base, pos + 1 - page * 64, tid);
+        load_page<HD, kFlashThreads>(smem, (S + st) * TILE, a.v_pool + base, pos + 1 - page * 64, tid);
+      }
+      cp_async_commit();
+    };
     for (int i = tid; i < 16 * (HD / 8); i += kFlashThreads) {
       const int row = i / (HD / 8), ch = i % (HD / 8);
       if (row < rows)
@@ -327,33 +341,22 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       else
         *reinterpret_cast<uint4*>(sQ_ptr + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
     }
-    {
-      const size_t base = ((size_t)page_of(my_lo) * a.kv_heads + kh) * 64 * HD;
-      load_page<HD, kFlashThreads>(smem, 0, a.k_pool + base, pos + 1 - my_lo * 64, tid);
-      load_page<HD, kFlashThreads>(smem, 2 * TILE, a.v_pool + base, pos + 1 - my_lo * 64, tid);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
+    fetch(my_lo);            // group 0 also carries the queries
+    fetch(my_lo + 1);
     uint32_t qf[HD / 16][4];
-#pragma unroll
-    for (int kb = 0; kb < HD / 16; ++kb) {
-      const int row = lane & 15, col = kb * 16 + ((lane >> 4) << 3);
-      ldmatrix_x4(qf[kb], sQ + swz<HD>(row, col));
-    }
 
     for (int page = my_lo; page <= my_hi; ++page) {
-      const int stage = (page - my_lo) & 1;
-      if (page < my_hi) {
-        const size_t base = ((size_t)page_of(page + 1) * a.kv_heads + kh) * 64 * HD;
-        load_page<HD, kFlashThreads>(smem, (stage ^ 1) * TILE, a.k_pool + base, pos + 1 - (page + 1) * 64, tid);
-        load_page<HD, kFlashThreads>(smem, (2 + (stage ^ 1)) * TILE, a.v_pool + base, pos + 1 - (page + 1) * 64, tid);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
+      const int stage = (page - my_lo) % S;
+      fetch(page + 2);       // into the buffer that the page before this one has left
+      cp_async_wait<2>();    // all but the two newest groups: this page has landed
       __syncthreads();
+      if (page == my_lo) {
+#pragma unroll
+        for (int kb = 0; kb < HD / 16; ++kb) {
+          const int row = lane & 15, col = kb * 16 + ((lane >> 4) << 3);
+          ldmatrix_x4(qf[kb], sQ + swz<HD>(row, col));
+        }
+      }
       const int key0 = page * 64 + warp * 16;     // this warp's 16 keys of the page
       if (key0 <= pos && key0 + 15 >= key_lo) {
         const uint32_t kS = sK + stage * TILE, vS = sV + stage * TILE;
@@ -368,7 +371,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
           mma_bf16(s[0], qf[kb], kf[0], kf[1]);
           mma_bf16(s[1], qf[kb], kf[2], kf[3]);
         }
-        float mx = -INFINITY;      // every row of the tile is the same token: one mask for all
+        // every row of the tile is the same token (different heads): one mask serves all
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -381,7 +384,6 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
         float mxr[2];
         mxr[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         mxr[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-        (void)mx;
         float alpha[2], m_use[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -421,6 +423,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       }
       __syncthreads();
     }
+    cp_async_wait<0>();
   }
 
   // merge the four warps (each saw different keys) through shared memory
@@ -482,14 +485,32 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     const int row = idx / HD, d = idx % HD;
     const int head = head0 + row;
     const size_t base = ((size_t)seq * a.heads + head) * a.splits;
-    float m = -INFINITY;
-    for (int s2 = 0; s2 < a.splits; ++s2) m = fmaxf(m, __ldcg(a.part_ml + (base + s2) * 2));
-    const float m_use = m == -INFINITY ? 0.0f : m;
-    float l = 0.0f, acc = 0.0f;
-    for (int s2 = 0; s2 < a.splits; ++s2) {
-      const float f = exp2f(__ldcg(a.part_ml + (base + s2) * 2) - m_use);
-      l += __ldcg(a.part_ml + (base + s2) * 2 + 1) * f;
-      acc += __ldcg(a.part_o + (base + s2) * HD + d) * f;
+    // eight slices at a time, all loads issued before any is used (they come from L2, one latency per batch);
+    // a running maximum rescales what has been summed, as in the attention loop itself
+    float m = -INFINITY, l = 0.0f, acc = 0.0f;
+    for (int s0 = 0; s0 < a.splits; s0 += 8) {
+      float pm[8], pl[8], po[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool live = s0 + j < a.splits;
+        pm[j] = live ? __ldcg(a.part_ml + (base + s0 + j) * 2) : -INFINITY;
+        pl[j] = live ? __ldcg(a.part_ml + (base + s0 + j) * 2 + 1) : 0.0f;
+        po[j] = live ? __ldcg(a.part_o + (base + s0 + j) * HD + d) : 0.0f;
+      }
+      float m_new = m;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m_new = fmaxf(m_new, pm[j]);
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+      const float keep = exp2f(m - m_use);
+      l *= keep;
+      acc *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = exp2f(pm[j] - m_use);
+        l += pl[j] * f;
+        acc += po[j] * f;
+      }
+      m = m_new;
     }
     a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
   }
@@ -516,7 +537,7 @@ template <int HD>
 static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
   const int G = a.heads / a.kv_heads;
   const int row_tiles = (G + 15) / 16;
-  const int tiles_bytes = 4 * 64 * HD * 2 + 16 * HD * 2;
+  const int tiles_bytes = 2 * kDecodeStages * 64 * HD * 2 + 16 * HD * 2;
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * 4;
   const int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
   static bool configured = false;

@@ -22,7 +22,7 @@ static int g_pdl = -1;
 int pdl_mode() {
   if (g_pdl < 0) {
     const char* e = getenv("SLEUTH_B200_PDL");
-    g_pdl = e ? (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1)) : 0;
+    g_pdl = e ? (e[0] == '0' ? 0 : (e[0] == '1' ? 1 : 2)) : 2;   // default 2: measured fastest on a B200
   }
   return g_pdl;
 }

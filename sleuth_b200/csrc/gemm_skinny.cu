@@ -62,8 +62,10 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // bfloat16(x * gain) and the factor is applied to the float32 sums in the epilogue. The sum of squares is
 // gathered from the same loads that feed the product, so the norm costs no extra pass, no extra kernel and no
 // wait in front of the product.
+// Two blocks per SM are asked for where a warp multiplies a single tile of weight rows (the narrow matrices, whose
+// blocks are many and short): measured faster there, slower for the two-tile shapes.
 template <int NF, int MODE, bool NORM>
-__global__ void __launch_bounds__(kSkinnyWarps * 32, 2) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1) ? 2 : 1) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   constexpr int kUnroll = unroll_for(TILES);
   __shared__ float red[kSkinnyWarps][TILES][16][8 + 1];

@@ -127,12 +127,14 @@ def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> 
     GPU a few times over, never more than a sequence can have pages. It depends on the batch size
     only, not on the lengths, so a captured step stays valid as sequences grow."""
     blocks = max(1, n_seqs * kv_heads * ((group + 15) // 16))
-    # three blocks of this kernel fit an SM (shared memory): 148 * 3 run at once. All slices should run in one
-    # wave, or else in whole waves.
-    resident = 148 * 3
+    # two blocks of this kernel fit an SM (100 KB of shared memory each at head size 128): 148 * 2 run at once.
+    # All slices should run in one wave.
+    resident = 148 * 2
     if blocks >= resident:
         return 1
-    return max(1, min(resident // blocks, 64, table_stride))
+    # merging the slices costs a few microseconds that grow with their number: a slice should hold at least
+    # four pages of the longest sequence
+    return max(1, min(resident // blocks, 64, max(1, table_stride // 4)))
 
 
 def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
