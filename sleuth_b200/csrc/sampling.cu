@@ -15,6 +15,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "no_alloc.h"
 
 namespace slb {
 
@@ -298,6 +299,44 @@ extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit
   launch(argmax_final_kernel, dim3(rows), dim3(32), 0, s, part_v, part_i, out);
   return check_launch("argmax");
 }
+
+// ---------------------------------------------------------------- argmax without any allocation ----
+// See no_alloc.h. The slices' partial results live in a fixed array inside the library image instead of in
+// memory the caller hands over. In host code the array's name is only a handle: its device address is asked
+// for once per device (cudaGetSymbolAddress, with that device current) and kept.
+constexpr int kStaticArgmaxRows = SLB_ARGMAX_STATIC_MAX_ROWS;
+static __device__ __align__(256) unsigned int g_argmax_scratch[2 * kStaticArgmaxRows * kArgmaxChunks];
+static void* g_argmax_scratch_addr[64] = {nullptr};
+
+extern "C" int slb_argmax_static(const float* logits, long long ld, int rows, int limit, int* out, void* stream) {
+  SLB_REQUIRE(rows >= 0 && limit > 0 && ld >= limit, "argmax_static: rows=%d limit=%d ld=%lld", rows, limit, ld);
+  SLB_REQUIRE(rows <= kStaticArgmaxRows,
+              "argmax_static: %d rows are more than the built-in scratch array holds (%d); use slb_argmax with scratch "
+              "memory of your own", rows, kStaticArgmaxRows);
+  if (rows == 0) return 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(2, "argmax_static: no usable current device (%s)", cudaGetErrorString(e));
+  if (g_argmax_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_argmax_scratch);     // first call on this device; not during stream capture
+    if (e != cudaSuccess || p == nullptr)
+      return fail(2, "argmax_static: cannot find the scratch array on device %d: %s", dev, cudaGetErrorString(e));
+    g_argmax_scratch_addr[dev] = p;
+  }
+  float* part_v = (float*)g_argmax_scratch_addr[dev];
+  int* part_i = (int*)g_argmax_scratch_addr[dev] + (size_t)kStaticArgmaxRows * kArgmaxChunks;
+  cudaStream_t s = (cudaStream_t)stream;
+  // every slot that the second stage reads is written by the first stage of the same call, so nothing left in
+  // the array by an earlier call is ever read and nothing has to be cleared
+  launch(argmax_partial_kernel, dim3(kArgmaxChunks, rows), dim3(kArgmaxThreads), 0, s, logits, ld, limit, part_v, part_i);
+  int rc = check_launch("argmax_static (slices)");
+  if (rc) return rc;
+  launch(argmax_final_kernel, dim3(rows), dim3(32), 0, s, (const float*)part_v, (const int*)part_i, out);
+  return check_launch("argmax_static");
+}
+
+extern "C" int slb_argmax_static_max_rows() { return kStaticArgmaxRows; }
 
 extern "C" int slb_sample(const float* logits, long long ld, int rows, int limit, float temperature, int top_k,
                           float top_p, float min_p, const float* uniform, int* out, void* stream) {
