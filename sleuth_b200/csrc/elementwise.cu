@@ -5,12 +5,16 @@ namespace slb {
 
 // x[t, :] = table[ids[t], :] * scale, into the float32 residual stream.
 // (Token rows looked up without scaling unless the model sets one: sleuth/forge/model/transformer.py:345-348.)
+// With `map`, row t takes token ids[map[t]]: a decode step can then read the tokens the sampler left on the
+// device for the previous batch, whose rows need not be this batch's rows.
 template <typename TW>
-__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
-                             int dim, float scale) {
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ map, const TW* __restrict__ table,
+                             float* __restrict__ x, int dim, int vocab, float scale) {
   pdl_enter();
   const int t = blockIdx.x;
-  const TW* row = table + (size_t)ids[t] * dim;
+  int tok = ids[map ? map[t] : t];
+  tok = min(max(tok, 0), vocab - 1);
+  const TW* row = table + (size_t)tok * dim;
   float* out = x + (size_t)t * dim;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
@@ -137,16 +141,16 @@ static int norm_threads(int dim) {
 
 using namespace slb;
 
-extern "C" int slb_embed(const int* ids, const void* table, int table_dtype, float* x, int tokens, int dim,
-                         float scale, void* stream) {
-  SLB_REQUIRE(tokens >= 0 && dim > 0, "embed: tokens=%d dim=%d", tokens, dim);
+extern "C" int slb_embed(const int* ids, const int* map, const void* table, int table_dtype, float* x, int tokens,
+                         int dim, int vocab, float scale, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0, "embed: tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = dim >= 256 ? 256 : 64;
   if (table_dtype == kF32)
-    launch(embed_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, (const float*)table, x, dim, scale);
+    launch(embed_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, map, (const float*)table, x, dim, vocab, scale);
   else if (table_dtype == kBF16)
-    launch(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, x, dim, scale);
+    launch(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, ids, map, (const __nv_bfloat16*)table, x, dim, vocab, scale);
   else
     return fail(1, "embed: unknown dtype %d", table_dtype);
   return check_launch("embed");

@@ -39,6 +39,7 @@ class StepBatch:
     rows: torch.Tensor
     tables: list
     floats: torch.Tensor | None = None      # [n] float32 scratch for the sampler's uniform numbers
+    ids_map: torch.Tensor | None = None     # decode steps: row t reads token_ids[ids_map[t]]
     host_counts: list = field(default_factory=list)
     host_past: list = field(default_factory=list)
     host_slots: list = field(default_factory=list)
@@ -54,6 +55,7 @@ class MetaStager:
     """Packs a step's tables, uploads them in one copy, and returns a ``StepBatch`` of device views."""
 
     RING = 4
+    FEED = 1024      # int32 slots at the start of the buffer where decode steps find their tokens
 
     def __init__(self, device, n_groups: int, stride: int, capacity: int = 1 << 16):
         self.device = torch.device(device)
@@ -76,9 +78,9 @@ class MetaStager:
 
     def layout(self, n: int, T: int, W: int, n_floats: int):
         """Offsets (in int32 elements) of every region for a batch of these sizes."""
-        off, o = {}, 0
+        off, o = {}, self.FEED
         for name, size in (("token_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_start", n + 1), ("past", n),
-                           ("counts", n), ("slots", n), ("rows", W), ("floats", n_floats)):
+                           ("counts", n), ("slots", n), ("rows", W), ("floats", n_floats), ("ids_map", n)):
             off[name] = (o, size)
             o += _round(max(size, 1))
         for g in range(self.n_groups):
@@ -86,9 +88,23 @@ class MetaStager:
             o += _round(n * self.stride)
         return off, o
 
-    def upload(self, slots, pasts, counts, tokens: np.ndarray, rows: np.ndarray, tables: list[np.ndarray],
-               floats: np.ndarray | None = None, stream: torch.cuda.Stream | None = None) -> StepBatch:
-        n, T, W = len(slots), int(tokens.shape[0]), int(rows.shape[0])
+    @property
+    def feed(self) -> torch.Tensor:
+        """The device-side token feed: a decode step reads its tokens from here (through ``ids_map``), and the
+        sampler may write the tokens it chooses straight into it for the next step."""
+        return self.dev[:self.FEED]
+
+    def upload(self, slots, pasts, counts, tokens: np.ndarray | None, rows: np.ndarray, tables: list[np.ndarray],
+               floats: np.ndarray | None = None, stream: torch.cuda.Stream | None = None,
+               feed_map: np.ndarray | None = None) -> StepBatch:
+        """tokens: this step's token ids from the host. For a decode step (one token per sequence, at most FEED
+        sequences) they go to the feed region; with ``tokens=None`` the feed is left as the sampler filled it and
+        ``feed_map[i]`` says which feed slot holds sequence i's token."""
+        n, W = len(slots), int(rows.shape[0])
+        T = int(sum(counts))
+        via_feed = feed_map is not None or (T == n and n <= self.FEED)
+        if tokens is None and feed_map is None:
+            raise ValueError("a step needs its tokens: from the host, or a map into the device-side feed")
         nf = 0 if floats is None else int(floats.shape[0])
         off, total = self.layout(n, T, W, nf)
         if total > self.cap:
@@ -111,7 +127,14 @@ class MetaStager:
             if size:
                 host[o:o + size] = arr
 
-        put("token_ids", tokens)
+        first = self.FEED                       # the copy starts here unless the host supplies feed contents
+        if via_feed:
+            if tokens is not None:
+                host[:n] = tokens
+                first = 0
+            put("ids_map", np.arange(n, dtype=np.int32) if feed_map is None or tokens is not None else feed_map)
+        else:
+            put("token_ids", tokens)
         put("tok_seq", seq_of)
         put("tok_pos", pos_of)
         put("seq_start", starts)
@@ -128,8 +151,8 @@ class MetaStager:
 
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(st):
-            self.dev[:total].copy_(self.hosts[i][:total], non_blocking=True)
-            self.last_upload_bytes = 4 * total
+            self.dev[first:total].copy_(self.hosts[i][first:total], non_blocking=True)
+            self.last_upload_bytes = 4 * (total - first)
             ev = torch.cuda.Event()
             ev.record(st)
         self.events[i] = ev
@@ -140,7 +163,8 @@ class MetaStager:
 
         fl = view("floats").view(torch.float32) if nf else None
         return StepBatch(
-            n=n, T=T, stream=st.cuda_stream, token_ids=view("token_ids"), tok_seq=view("tok_seq"),
+            n=n, T=T, stream=st.cuda_stream, token_ids=self.feed if via_feed else view("token_ids"),
+            ids_map=view("ids_map") if via_feed else None, tok_seq=view("tok_seq"),
             tok_pos=view("tok_pos"), seq_start=view("seq_start"), past=view("past"), counts=view("counts"),
             slots=view("slots"), rows=view("rows"),
             tables=[view(f"table{g}").view(n, self.stride) for g in range(self.n_groups)], floats=fl,

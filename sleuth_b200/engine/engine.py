@@ -145,6 +145,20 @@ class Engine:
     def decode(self, slots, tokens):
         return self.stepper.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, tokens)])
 
+    pipelined = True      # the generation loop may run one step ahead of the host (engine/generate.py)
+
+    def choose_later(self, logits, cfg, uniforms, vocab_limit):
+        """Choose into the device-side token feed and start copying the tokens to the host."""
+        u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
+        if logits.shape[0] > self.stepper.feed.numel():
+            tokens = self.sampler.choose(logits, cfg, u, vocab_limit)
+        else:
+            tokens = self.sampler.choose(logits, cfg, u, vocab_limit, out=self.stepper.feed)
+        return self.sampler.to_host_later(tokens)
+
+    def decode_fed(self, slots, feed_map):
+        return self.stepper.decode_fed(slots, feed_map)
+
     def choose(self, logits, cfg, uniforms, vocab_limit, recent, banned) -> list[int]:
         u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
         return self.sampler.to_host(self.sampler.choose(logits, cfg, u, vocab_limit, recent, banned))
@@ -175,6 +189,7 @@ class Engine:
             stop_ids = set(getattr(self.config, "stop_ids", ()))
         before = self.stepper.use_graphs
         self.stepper.use_graphs = before and cuda_graph
+        self.pipelined = len(prompts) <= self.stepper.feed.numel() and max_batch <= self.stepper.feed.numel()
         try:
             results = generate_batches(self, prompts, max_new_tokens, sampling, stop_ids, vocab_limit, seed, on_token,
                                        max_batch)

@@ -60,6 +60,10 @@ class Backend(Protocol):
     def pages_needed(self, slots: Sequence[int], new_lengths: Sequence[int]) -> int: ...
     def length(self, slot: int) -> int: ...
     def sync(self) -> None: ...
+    # optional, for the pipelined loop (``pipelined = True``):
+    #   choose_later(logits, cfg, uniforms, vocab_limit) -> callable giving the tokens once they are on the host;
+    #       the tokens also stay on the device, row i of them in feed slot i
+    #   decode_fed(slots, feed_map) -> logits: sequence i continues with the token in feed slot feed_map[i]
 
 
 @dataclass
@@ -111,9 +115,13 @@ def generate_batches(backend: Backend, prompts: Sequence[Sequence[int]], max_new
     results: list[GenerationResult | None] = [None] * len(cleaned)
     if max_new_tokens <= 0:
         return [GenerationResult(p, [], "max_new_tokens", 0.0, 0.0) for p in cleaned]
+    # Penalties and n-gram bans need the newest token on the host before the next choice; everything else can run
+    # one step ahead of the host (see _run_batch_pipelined).
+    pipelined = getattr(backend, "pipelined", False) and not sampling.needs_context
+    run = _run_batch_pipelined if pipelined else _run_batch
     for batch in plan_batches([len(p) for p in cleaned], max_new_tokens, backend.max_len, backend.total_pages,
                               max_batch):
-        _run_batch(backend, batch, cleaned, results, max_new_tokens, sampling, stop_ids, vocab_limit, seed, on_token)
+        run(backend, batch, cleaned, results, max_new_tokens, sampling, stop_ids, vocab_limit, seed, on_token)
     return results  # type: ignore[return-value]
 
 
@@ -168,6 +176,74 @@ def _run_batch(backend, batch, prompts, results, max_new_tokens, sampling, stop_
             if not live:
                 break
             logits = backend.decode([q.slot for q in live], [q.new[-1] for q in live])
+    finally:
+        if held:
+            backend.close(sorted(held))
+
+
+def _run_batch_pipelined(backend, batch, prompts, results, max_new_tokens, sampling, stop_ids, vocab_limit, seed,
+                         on_token):
+    """The same decisions as ``_run_batch`` with the host one step behind the GPU.
+
+    The chosen tokens stay on the device and the next step reads them there, so step k + 1 is launched before the
+    host has seen the tokens of step k; the host then reads them while the GPU works. Whether a sequence goes on
+    is known without its newest token except for one reason, a stop token: a sequence that has just produced one
+    is therefore carried through one more step, whose result is thrown away. Its outputs, its stop reason and the
+    other sequences' results are exactly those of the step-by-step loop."""
+    slots = backend.open(len(batch))
+    rows = [_Live(r, s, prompts[r]) for r, s in zip(batch, slots)]      # in the order of the pending tokens
+    held = set(slots)
+    done: set[int] = set()                                               # requests that have ended
+
+    def uniforms(live, step):
+        return None if sampling.greedy else [uniform(seed, q.request, step) for q in live]
+
+    try:
+        backend.sync()
+        t0 = time.perf_counter()
+        logits = backend.prefill([q.slot for q in rows], [q.prompt for q in rows])
+        pending = backend.choose_later(logits, sampling, uniforms(rows, 0), vocab_limit)
+        t1 = None
+        k = 0                                   # index of the pending tokens among each sequence's new tokens
+        while rows:
+            # who is fed its pending token: decided from counts alone
+            why_not = {}
+            for q in rows:
+                if q.request in done:
+                    continue
+                if backend.length(q.slot) >= backend.max_len:
+                    why_not[q.request] = "context_full"
+                elif k + 1 >= max_new_tokens:
+                    why_not[q.request] = "max_new_tokens"
+            cont = [q for q in rows if q.request not in done and q.request not in why_not]
+            while cont and backend.pages_needed([q.slot for q in cont],
+                                                [backend.length(q.slot) + 1 for q in cont]) > backend.free_pages():
+                q = max(cont, key=lambda q: backend.length(q.slot))
+                cont.remove(q)
+                why_not[q.request] = "context_full"
+            next_pending = None
+            if cont:
+                index = {q.request: i for i, q in enumerate(rows)}
+                logits = backend.decode_fed([q.slot for q in cont], [index[q.request] for q in cont])
+                next_pending = backend.choose_later(logits, sampling, uniforms(cont, k + 1), vocab_limit)
+            # now the host catches up with the tokens of step k
+            tokens = pending()
+            now = time.perf_counter()
+            if t1 is None:
+                t1 = now
+            for q, tok in zip(rows, tokens):
+                if q.request in done:
+                    continue                    # carried along after its stop token: not its token any more
+                q.new.append(tok)
+                if on_token is not None:
+                    on_token(q.request, tok)
+                reason = "stop_token" if tok in stop_ids else why_not.get(q.request)
+                if reason is not None:
+                    done.add(q.request)
+                    _finish(backend, q, reason, results, t0, t1, now, held)
+            rows, pending, k = cont, next_pending, k + 1
+            if not any(q.request not in done for q in rows):
+                break
     finally:
         if held:
             backend.close(sorted(held))

@@ -65,7 +65,7 @@ class Model:
         b.stream = torch.cuda.current_stream().cuda_stream   # inside a graph capture this is the capture stream
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
-        self.embedding.forward(b.token_ids, x, b.stream)
+        self.embedding.forward(b.token_ids, x, b.stream, b.ids_map)
         for i, e in enumerate(self.spec.schedule):
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
             self.layers[e.layer].forward(x, b, view, ws)

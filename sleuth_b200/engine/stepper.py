@@ -145,16 +145,45 @@ class Stepper:
 
     # ------------------------------------------------------------------ decode ----
     def _decode(self, entries, slots, toks, floats) -> torch.Tensor:
+        tokens = np.asarray([int(t[0]) for t in toks], dtype=np.int32)
+        logits = self._decode_core(slots, tokens, None, floats)
+        n = len(slots)
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == n:
+            return logits
+        if not wanted:
+            return logits[:0]
+        return logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
+
+    def decode_fed(self, slots, feed_map) -> torch.Tensor:
+        """One token for each of ``slots``, taken from the device-side feed: sequence i reads
+        ``feed[feed_map[i]]``, where the sampler left the tokens it chose for the previous step's rows.
+        Returns the logits of every row (a view that the next step overwrites)."""
+        book = self.cache.book
+        slots = [int(s) for s in slots]
+        if len(slots) > self.meta.FEED:
+            raise ValueError(f"a device-fed step takes at most {self.meta.FEED} sequences")
+        for s in slots:
+            if int(book.lengths[s]) + 1 > self.max_len:
+                raise CacheFull(f"slot {s} would hold {int(book.lengths[s]) + 1} tokens; the longest sequence allowed "
+                                f"is {self.max_len}")
+        return self._decode_core(slots, None, np.asarray(feed_map, dtype=np.int32), None)
+
+    @property
+    def feed(self) -> torch.Tensor:
+        return self.meta.feed
+
+    def _decode_core(self, slots, tokens, feed_map, floats) -> torch.Tensor:
         book = self.cache.book
         n = len(slots)
         past = [int(book.lengths[s]) for s in slots]
         new_lens = [p + 1 for p in past]
         book.grow(slots, new_lens)
-        tokens = np.asarray([int(t[0]) for t in toks], dtype=np.int32)
         rows = np.arange(n, dtype=np.int32)
         if floats is None:
             floats = np.zeros(n, dtype=np.float32)
-        b = self.meta.upload(slots, past, [1] * n, tokens, rows, book.tables_for(slots), floats=floats)
+        b = self.meta.upload(slots, past, [1] * n, tokens, rows, book.tables_for(slots), floats=floats,
+                             feed_map=feed_map)
         self.last_batch = b
         if self._decode_logits is None or self._decode_logits.shape[0] < n:
             cap = max(n, 8 if self._decode_logits is None else 2 * self._decode_logits.shape[0])
@@ -166,28 +195,23 @@ class Stepper:
         if key != self._graph_key:
             self._graphs.clear()
             self._graph_key = key
-        graph = self._graphs.get(n)
+        gkey = (n, b.ids_map is not None)
+        graph = self._graphs.get(gkey)
         if graph is not None:
             graph.replay()
-            self.graph_kernel_launches += self._graph_own[n]
-        elif self.use_graphs and n <= self.max_graph_batch and n in self._seen_decode:
+            self.graph_kernel_launches += self._graph_own[gkey]
+        elif self.use_graphs and n <= self.max_graph_batch and gkey in self._seen_decode:
             before = ops.lib().launches
-            self._graphs[n] = self._capture(b, logits)
-            self._graph_own[n] = ops.lib().launches - before
+            self._graphs[gkey] = self._capture(b, logits)
+            self._graph_own[gkey] = ops.lib().launches - before
             ops.lib().launches = before          # captured, not run
-            self._graphs[n].replay()
-            self.graph_kernel_launches += self._graph_own[n]
+            self._graphs[gkey].replay()
+            self.graph_kernel_launches += self._graph_own[gkey]
         else:
             self.model.forward(b, self.cache, self.ws, logits)
-            self._seen_decode.add(n)
+            self._seen_decode.add(gkey)
         book.commit(slots, new_lens)
-
-        wanted = [i for i, e in enumerate(entries) if len(e.want)]
-        if len(wanted) == n:
-            return logits
-        if not wanted:
-            return logits[:0]
-        return logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
+        return logits
 
     def _capture(self, b, logits):
         torch.cuda.synchronize(self.device)

@@ -128,7 +128,7 @@ def build(verbose: bool = True) -> Path:
 I, L, F, P = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
 _SIGNATURES = {
-    "slb_embed": [P, P, I, P, I, I, F, P],
+    "slb_embed": [P, P, P, I, P, I, I, I, F, P],
     "slb_rmsnorm": [P, P, P, I, P, I, I, F, P],
     "slb_add": [P, P, I, L, P],
     "slb_swiglu": [P, P, I, I, I, P],

@@ -41,12 +41,16 @@ def _cuda(*tensors) -> None:
             _need(t.is_contiguous(), f"tensor of shape {tuple(t.shape)} must be contiguous")
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0, stream=None) -> None:
-    _cuda(ids, table, x)
+def embed(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0, stream=None,
+          ids_map: torch.Tensor | None = None) -> None:
+    """x[t] = table[ids[t]] * scale, or table[ids[ids_map[t]]] with a map. Ids outside the table are clamped
+    (the caller checks host ids; ids that a sampler left on the device lie inside by construction)."""
+    _cuda(ids, table, x, ids_map)
     T, d = x.shape
-    _need(ids.dtype == torch.int32 and ids.numel() >= T, "embed: ids must be int32, one per row of x")
+    _need(ids.dtype == torch.int32 and (ids_map is not None or ids.numel() >= T), "embed: ids must be int32, one per row of x")
+    _need(ids_map is None or (ids_map.dtype == torch.int32 and ids_map.numel() >= T), "embed: the map is int32, one per row")
     _need(table.shape[1] == d and x.dtype == torch.float32 and table.dtype in DT, "embed: shapes or dtypes disagree")
-    lib().call("slb_embed", _p(ids), _p(table), DT[table.dtype], _p(x), T, d, float(scale),
+    lib().call("slb_embed", _p(ids), _p(ids_map), _p(table), DT[table.dtype], _p(x), T, d, table.shape[0], float(scale),
                stream if stream is not None else current_stream())
 
 

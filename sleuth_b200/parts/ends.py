@@ -23,8 +23,8 @@ class TokenEmbedding(Part):
     def bind(self, t):
         self.table = t["weight"]
 
-    def forward(self, ids, x, stream=None):
-        ops.embed(ids, self.table, x, self.spec.scale, stream)
+    def forward(self, ids, x, stream=None, ids_map=None):
+        ops.embed(ids, self.table, x, self.spec.scale, stream, ids_map)
 
 
 class LMHead(Part):

@@ -30,7 +30,7 @@ class Sampler:
 
     def choose(self, logits: torch.Tensor, cfg: SamplingConfig, uniform: torch.Tensor | np.ndarray | None = None,
                vocab_limit: int | None = None, recent: list[list[int]] | None = None,
-               banned: list[list[int]] | None = None) -> torch.Tensor:
+               banned: list[list[int]] | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         """Tokens for the rows of ``logits`` [n, vocab] as a device int32 tensor [n].
 
         ``logits`` is changed in place when a ban list or a repetition penalty applies. ``recent``
@@ -49,7 +49,7 @@ class Sampler:
                 ban_t, nban_t = self._ragged(banned)
         if rec_t is not None or ban_t is not None:
             ops.penalize(logits, limit, rec_t, nrec_t, cfg.repetition_penalty, ban_t, nban_t, stream)
-        out = self._out[:n]
+        out = self._out[:n] if out is None else out[:n]
         if cfg.greedy:
             ops.argmax(logits, limit, out, self._scratch, stream)
         else:
@@ -65,6 +65,25 @@ class Sampler:
         self._host[:n].copy_(tokens, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return self._host[:n].tolist()
+
+    def to_host_later(self, tokens: torch.Tensor):
+        """Start copying ``tokens`` to the host; returns a function that waits for the copy and gives the list.
+        Up to four such copies may be pending."""
+        n = tokens.numel()
+        if not hasattr(self, "_ring"):
+            self._ring, self._turn = [torch.zeros(4096, dtype=torch.int32).pin_memory() for _ in range(4)], 0
+        buf = self._ring[self._turn]
+        self._turn = (self._turn + 1) % len(self._ring)
+        if n > buf.numel():
+            raise ValueError(f"{n} tokens are more than a pending copy holds ({buf.numel()})")
+        buf[:n].copy_(tokens, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+
+        def wait() -> list[int]:
+            ev.synchronize()
+            return buf[:n].tolist()
+        return wait
 
     def _ragged(self, lists: list[list[int]]):
         width = max(1, max(len(x) for x in lists))

@@ -55,6 +55,17 @@ class ScriptedBackend:
             out.append(self.script(seq[:p], len(seq) - p))
         return out
 
+    # ---- the pipelined protocol: tokens stay "on the device" (self.feed), the host gets them one step late ----
+    def choose_later(self, logits, cfg, uniforms, vocab_limit):
+        tokens = self.choose(logits, cfg, uniforms, vocab_limit, None, None)
+        self.feed = list(tokens)
+        self.log.append(("choose_later", len(tokens)))
+        return lambda: list(tokens)
+
+    def decode_fed(self, slots, feed_map):
+        self.log.append(("decode", tuple(slots)))
+        return self._append(slots, [[self.feed[i]] for i in feed_map])
+
     def free_pages(self):
         return self.book.groups[0].pool.free
 
@@ -72,6 +83,13 @@ def count_up(prompt, k):
     return (prompt[-1] + k + 1) % 100
 
 
+@pytest.fixture(params=["step by step", "one step ahead"], autouse=True)
+def loop_mode(request, monkeypatch):
+    """Every test of the loop runs twice: with the host waiting for each token, and with the GPU one step ahead."""
+    monkeypatch.setattr(ScriptedBackend, "pipelined", request.param == "one step ahead", raising=False)
+    return request.param
+
+
 def test_unequal_prompts_stop_tokens_and_early_finishers():
     be = ScriptedBackend(count_up)
     prompts = [[10], [20, 21, 22], [50, 51]]                      # sequence 0 meets 13 at its third token
@@ -83,7 +101,10 @@ def test_unequal_prompts_stop_tokens_and_early_finishers():
     assert res[2].new_ids == [52, 53, 54, 55] and res[2].stop_reason == "stop_token"
     assert [r.prompt_ids for r in res] == prompts
     decodes = [e for e in be.log if e[0] == "decode"]
-    assert [len(e[1]) for e in decodes] == [3, 3, 2, 1, 1]      # the batch shrinks as sequences end
+    if be.pipelined:      # a sequence that met its stop token is carried through one more step
+        assert [len(e[1]) for e in decodes] == [3, 3, 3, 2, 1]
+    else:
+        assert [len(e[1]) for e in decodes] == [3, 3, 2, 1, 1]  # the batch shrinks as sequences end
     assert be.book.free_slots == be.book.max_slots and be.book.pages_in_use() == [0]
     assert [t for r, t in seen if r == 2] == [52, 53, 54, 55]
 
