@@ -1,0 +1,338 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: C[M, N] = X[M, K] * W[N, K]^T for many rows (prefill).
+//
+// One block computes a 128 x BN tile of C (BN = 128 or 256 columns):
+//   * warp 0, one lane: the producer. For every 64-wide slice of K it asks TMA (cp.async.bulk.tensor) for the
+//     128 x 64 tile of X and the BN x 64 tile of W; both arrive in shared memory in the 128-byte-swizzled K-major
+//     layout that the tensor core reads, and their arrival is counted on the stage's "full" mbarrier.
+//   * warp 1, one lane: the MMA issuer. It waits for a full stage and issues four tcgen05.mma (K = 16 each,
+//     M = 128, N = BN) that accumulate into tensor memory (TMEM), then tcgen05.commit makes the stage's "empty"
+//     mbarrier fire when those MMAs have read the stage. After the last slice a commit arms the "done" mbarrier.
+//   * all four warps: the epilogue. Warp w reads rows 32w .. 32w+31 of the accumulator (tcgen05.ld, 32 columns at a
+//     time), applies the epilogue and stores: bfloat16, float32, float32 accumulate (residual stream), or the gated
+//     activation silu(gate) * up when W holds the gate rows followed by the up rows (sleuth/forge/model/mlp.py:37-40);
+//     the block then multiplies X by 128 gate rows and the 128 matching up rows in one N = 256 instruction.
+// Rows, columns and K beyond the matrices are zero-filled by TMA and masked at the store, so every M, N and every K
+// that is a multiple of 8 is taken. (The reference calls a library here: nn.Linear, sleuth/forge/model/attention.py:106-108.)
+//
+// Every wait is bounded: a thread that waits longer than a few seconds' worth of polls records where in
+// `status` and leaves its loop; the block then still frees its tensor memory and returns. TMA loads never use
+// cluster multicast.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace slb {
+
+constexpr int kTcBM = 128;
+constexpr int kTcBK = 64;             // bf16 elements per slice: 128 bytes, one swizzle row
+constexpr int kTcStages = 4;
+constexpr int kTcThreads = 128;
+constexpr uint32_t kSpinLimit = 4000000u;
+
+enum TcMode : int { kTcBf16 = 0, kTcF32 = 1, kTcAddF32 = 2, kTcSwiglu = 3 };
+
+struct TcArgs {
+  void* C;
+  int M, N, K, ldc, mode;
+  int up_row0;          // kTcSwiglu: first up row in W (= number of gate rows)
+  int* status;          // 0 = fine; else a code saying which wait gave up
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Polls the barrier's phase; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);         // start address
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset: 8 rows * 128 bytes
+  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                         // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M x N.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2, STAGE = A_BYTES + B_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcStages * STAGE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 1);
+  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * kTcStages, done = empty0 + 8 * kTcStages;
+  const uint32_t tiles = smem_addr(smem);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kTcBM;
+  const bool gated = a.mode == kTcSwiglu;
+  const int n0 = blockIdx.x * (gated ? BN / 2 : BN);      // first output column of this block
+  const int k_tiles = (a.K + kTcBK - 1) / kTcBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {     // one warp allocates BN columns of tensor memory for the accumulator
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  pdl_launch_dependents();
+  pdl_wait();          // X is the previous kernel's output
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer ----
+    for (int kt = 0; kt < k_tiles; ++kt) {
+      const int s = kt % kTcStages;
+      if (kt >= kTcStages && !mbar_wait(empty0 + 8 * s, ((kt / kTcStages) - 1) & 1)) {
+        atomicExch(a.status, 1);
+        break;
+      }
+      const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
+      mbar_expect_tx(full0 + 8 * s, STAGE);
+      tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
+      if (gated) {
+        tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
+        tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
+      } else {
+        tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
+        if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = instr_desc(kTcBM, BN);
+    bool ok = true;
+    for (int kt = 0; kt < k_tiles && ok; ++kt) {
+      const int s = kt % kTcStages;
+      if (!mbar_wait(full0 + 8 * s, (kt / kTcStages) & 1)) {
+        atomicExch(a.status, 2);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
+      const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+#pragma unroll
+      for (int k4 = 0; k4 < kTcBK / 16; ++k4)      // 16 elements = 32 bytes further along K inside the swizzle row
+        mma_bf16_ss(tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+      mma_commit(empty0 + 8 * s);                  // fires when these MMAs have read the stage
+    }
+    mma_commit(done);                              // fires when every MMA issued so far has completed
+  }
+
+  // ---- epilogue: all four warps ----
+  __syncwarp();
+  bool ready = true;
+  if (lane == 0) ready = mbar_wait(done, 0);
+  ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+  if (!ready && lane == 0) atomicExch(a.status, 3);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (ready) {
+    const int row = m0 + warp * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const int out_cols = gated ? BN / 2 : BN;
+    for (int c = 0; c < out_cols; c += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + c, r);
+      if (gated) {
+        uint32_t u[32];
+        tmem_ld32(lane_base + BN / 2 + c, u);
+        if (row < a.M) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n0 + c + j < a.N) {
+              const float g = __uint_as_float(r[j]);
+              dst[j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * __uint_as_float(u[j]));
+            }
+          }
+        }
+      } else if (row < a.M) {
+        const bool full = n0 + c + 32 <= a.N;
+        if (a.mode == kTcBf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + n0 + c;
+          if (full && (a.ldc % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+              v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+              v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+              *reinterpret_cast<uint4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c + j < a.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(a.C) + (size_t)row * a.ldc + n0 + c;
+          if (full && (a.ldc % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                     __uint_as_float(r[j + 3]));
+              if (a.mode == kTcAddF32) {
+                const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c + j < a.N) dst[j] = (a.mode == kTcAddF32 ? dst[j] : 0.0f) + __uint_as_float(r[j]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+}
+
+// ------------------------------------------------------------------------------------ host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix seen through boxes of box_rows x 64 elements, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(2, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(2, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <int BN>
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s) {
+  const int smem = kTcStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kTcStages + 1) * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(2, "gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int cols_per_block = a.mode == kTcSwiglu ? BN / 2 : BN;
+  dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (a.M + kTcBM - 1) / kTcBM);
+  launch_prefetching(gemm_tc_kernel<BN>, grid, dim3(kTcThreads), (size_t)smem, s, mx, mw, a);
+  return check_launch("gemm_tc");
+}
+
+}  // namespace slb
+
+using namespace slb;
+
+extern "C" int slb_gemm_tc_supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
+
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds N gate rows then N up
+// rows; C is [M, N] bfloat16). `status` is a device int that the caller zeroed; the kernel writes a non-zero code
+// there if one of its bounded waits gave up (the result is then invalid and the caller must say so).
+extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, int* status,
+                           void* stream) {
+  SLB_REQUIRE(slb_gemm_tc_supported(M, N, K), "gemm_tc: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
+  SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N && status != nullptr, "gemm_tc: mode=%d ldc=%d N=%d", mode, ldc, N);
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0),
+              "gemm_tc: X, W and C must be 16-byte aligned");
+  const bool gated = mode == kTcSwiglu;
+  // 256 columns per block when the matrix is wide enough to fill the GPU that way, else 128
+  const bool wide = gated || ((long long)((M + 127) / 128) * ((N + 255) / 256) >= 120);
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, X, M, K, kTcBM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, gated ? 2ll * N : N, K, 128);
+  if (rc) return rc;
+  TcArgs a;
+  a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.mode = mode; a.up_row0 = N; a.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  return wide ? launch_tc<256>(mx, mw, a, s) : launch_tc<128>(mx, mw, a, s);
+}

@@ -23,6 +23,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import os
+
 import numpy as np
 import torch
 
@@ -54,6 +56,7 @@ class Stepper:
         self._seen_decode: set = set()
         self._decode_logits: torch.Tensor | None = None
         self._graph_key = None
+        self.check_kernels = os.environ.get("SLEUTH_B200_CHECK", "0") == "1"   # read the kernels' status word after each step
         self._graph_own: dict = {}          # own kernel launches captured in each graph
         self.graph_kernel_launches = 0      # own kernel launches replayed through graphs so far
         ops.lib()   # build or load the kernels now; fail here, loudly, if that is impossible
@@ -106,6 +109,8 @@ class Stepper:
             self._run_chunk(entries, slots, toks, chunk, out, out_base)
             for i, start, take in chunk:
                 done[i] = start + take
+        if self.check_kernels:
+            ops.gemm_tc_check(self.device)
         return out
 
     # ------------------------------------------------------------------ chunks ----

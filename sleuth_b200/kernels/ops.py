@@ -240,6 +240,46 @@ def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.T
                stream if stream is not None else current_stream())
 
 
+def tc_supported(M: int, N: int, K: int) -> bool:
+    """Whether the tcgen05/TMA product kernel takes this problem."""
+    return M >= 1 and N >= 1 and K >= 8 and K % 8 == 0
+
+
+_TC_STATUS: dict = {}
+
+
+def _tc_status(device) -> torch.Tensor:
+    key = str(device)
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None) -> None:
+    """out = x[M, K] @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulation in tensor memory).
+    mode as for ``gemm_skinny``: "bf16" / "f32" store, "add" into a float32 ``out``, "swiglu" with w = [gate; up]."""
+    _cuda(x, w, out)
+    M, K = x.shape
+    N = out.shape[1]
+    _need(x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape[0] == M, "gemm_tc: shapes or dtypes")
+    _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_tc: weight rows")
+    _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_tc: output dtype")
+    lib().call("slb_gemm_tc", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode], _p(_tc_status(x.device)),
+               stream if stream is not None else current_stream())
+
+
+def gemm_tc_check(device) -> None:
+    """Raise if a tcgen05 product kernel gave up one of its bounded waits since the last check (synchronises)."""
+    st = _TC_STATUS.get(str(torch.device(device)))
+    if st is None:
+        return
+    code = int(st.item())
+    if code:
+        st.zero_()
+        raise RuntimeError(f"gemm_tc: a wait inside the kernel gave up (code {code}: 1 = free stage, 2 = loaded "
+                           f"stage, 3 = finished accumulator); its results are not valid")
+
+
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:
     _cuda(logits, recent, n_recent, banned, n_banned)
     R = logits.shape[0]

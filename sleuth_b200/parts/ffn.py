@@ -8,6 +8,7 @@ import torch
 
 from ..kernels import ops
 from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
+from . import linear
 from .linear import Linear
 from .spec import GatedMLPSpec
 
@@ -45,6 +46,9 @@ class GatedMLP(Part):
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream)
             else:
                 ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
+        elif (self.ctx.dtype == torch.bfloat16 and linear.USE_TC
+              and ops.tc_supported(T, self.spec.intermediate, self.spec.hidden)):
+            ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
             ops.swiglu(gu, act, b.stream)

@@ -4,8 +4,11 @@
   output element sums over k in one fixed order whatever the number of rows.
 * bfloat16 run, up to 16 rows (decode steps): the package's weight-streaming tensor-core kernel
   (``csrc/gemm_skinny.cu``), with the residual add or the float32 store in its epilogue.
-* bfloat16 run, more rows: a library product with float32 accumulation (cuBLAS through ``torch.mm``),
-  as the reference's ``nn.Linear`` (sleuth/forge/model/attention.py:106-108).
+* bfloat16 run, more rows: the package's tcgen05/TMA kernel (``csrc/gemm_tc.cu``: operands by TMA into
+  swizzled shared memory, accumulation in tensor memory, the same epilogues). Only when the inner
+  dimension is no multiple of 8 (TMA needs 16-byte rows) does the product go to a library (cuBLAS through
+  ``torch.mm``, float32 accumulation), as the reference's ``nn.Linear`` always does
+  (sleuth/forge/model/attention.py:106-108).
 
 ``into`` adds the product to a float32 tensor (the residual stream) instead of returning it.
 """
@@ -17,6 +20,12 @@ import torch
 from ..kernels import ops
 from .base import Normed
 
+
+import os
+
+# SLEUTH_B200_GEMM=library sends the many-row bfloat16 products to cuBLAS instead of this package's tcgen05 kernel
+# (for comparison; K that is no multiple of 8 goes there in any case).
+USE_TC = os.environ.get("SLEUTH_B200_GEMM", "own") != "library"
 
 _MODE: dict = {}
 
@@ -83,6 +92,15 @@ class Linear:
             if out is None:
                 out = ws.take((M, self.out_features), want)
             ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream)
+            return out
+        if USE_TC and ops.tc_supported(M, self.out_features, self.in_features):
+            if into is not None:
+                ops.gemm_tc(h, self.weight, into, "add", stream)
+                return into
+            want = out_dtype or (out.dtype if out is not None else self.dtype)
+            if out is None:
+                out = ws.take((M, self.out_features), want)
+            ops.gemm_tc(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream)
             return out
         if into is not None:
             mode = _accumulate_mode(h.device)
