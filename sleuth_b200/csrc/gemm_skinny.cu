@@ -1,4 +1,4 @@
-// Matrix product for a handful of rows: C[M, N] = X[M, K] * W[N, K]^T with M <= 16, bfloat16 in, float32 accumulation.
+// Matrix product for a handful of rows: C[M, N] = X[M, K] * W[N, K]^T with M <= 64, bfloat16 in, float32 accumulation.
 //
 // A decode step multiplies a few token rows by every weight matrix, so the time is the time to stream the weights
 // from memory once. The kernel is built around that: each lane fetches 16 contiguous bytes of a weight row straight
@@ -64,11 +64,15 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // wait in front of the product.
 // Two blocks per SM are asked for where a warp multiplies a single tile of weight rows (the narrow matrices, whose
 // blocks are many and short): measured faster there, slower for the two-tile shapes.
-template <int NF, int MODE, bool NORM>
-__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1) ? 2 : 1) gemm_skinny_kernel(SkinnyArgs a) {
+// MT: token rows come in tiles of 16; MT = 1 serves up to 16 rows, MT = 2 up to 32, MT = 4 up to 64. With MT > 1
+// the token fragments are fetched as they are needed (they sit in L1 after the first block of an SM has read them)
+// while the weight loads still go out in one batch.
+template <int NF, int MODE, bool NORM, int MT>
+__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : 1) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   constexpr int kUnroll = unroll_for(TILES);
-  __shared__ float red[kSkinnyWarps][TILES][16][8 + 1];
+  static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
+  __shared__ float red[kSkinnyWarps][TILES][16 * MT][8 + 1];
   __shared__ float ssq_part[kSkinnyWarps][16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -90,9 +94,11 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   const float* frow0 = (NORM && g < a.M) ? a.Xf + (size_t)g * a.K + 8 * t : nullptr;
   const float* frow1 = (NORM && g + 8 < a.M) ? a.Xf + (size_t)(g + 8) * a.K + 8 * t : nullptr;
 
-  float acc[TILES][4];
+  float acc[MT][TILES][4];
 #pragma unroll
-  for (int f = 0; f < TILES; ++f) acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.0f;
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int f = 0; f < TILES; ++f) acc[mt][f][0] = acc[mt][f][1] = acc[mt][f][2] = acc[mt][f][3] = 0.0f;
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
   uint4 w[kUnroll][TILES];
@@ -113,6 +119,25 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   float ssq0 = 0.0f, ssq1 = 0.0f;     // NORM: sums of squares of this lane's share of rows g and g + 8
   for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
     if (kb != kb_begin) fetch_weights(kb);
+    if (MT > 1) {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (kb + u >= kb_end) break;
+        const int off = (kb + u) * 32 + 8 * t;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const int r0 = 16 * mt + g, r1 = r0 + 8;
+          const uint4 xa = r0 < a.M ? *reinterpret_cast<const uint4*>(a.X + (size_t)r0 * a.K + off) : zero;
+          const uint4 xb = r1 < a.M ? *reinterpret_cast<const uint4*>(a.X + (size_t)r1 * a.K + off) : zero;
+#pragma unroll
+          for (int f = 0; f < TILES; ++f) {
+            mma_16816(acc[mt][f], xa.x, xb.x, xa.y, xb.y, w[u][f].x, w[u][f].y);
+            mma_16816(acc[mt][f], xa.z, xb.z, xa.w, xb.w, w[u][f].z, w[u][f].w);
+          }
+        }
+      }
+      continue;
+    }
     uint4 x0[kUnroll], x1[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -150,20 +175,22 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
     for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
       for (int f = 0; f < TILES; ++f) {
-        mma_16816(acc[f], x0[u].x, x1[u].x, x0[u].y, x1[u].y, w[u][f].x, w[u][f].y);
-        mma_16816(acc[f], x0[u].z, x1[u].z, x0[u].w, x1[u].w, w[u][f].z, w[u][f].w);
+        mma_16816(acc[0][f], x0[u].x, x1[u].x, x0[u].y, x1[u].y, w[u][f].x, w[u][f].y);
+        mma_16816(acc[0][f], x0[u].z, x1[u].z, x0[u].w, x1[u].w, w[u][f].z, w[u][f].w);
       }
     }
   }
 
   // accumulator layout: c0, c1 = (row g, cols 2t, 2t+1); c2, c3 = (row g+8, same cols)
 #pragma unroll
-  for (int f = 0; f < TILES; ++f) {
-    red[warp][f][g][2 * t] = acc[f][0];
-    red[warp][f][g][2 * t + 1] = acc[f][1];
-    red[warp][f][g + 8][2 * t] = acc[f][2];
-    red[warp][f][g + 8][2 * t + 1] = acc[f][3];
-  }
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int f = 0; f < TILES; ++f) {
+      red[warp][f][16 * mt + g][2 * t] = acc[mt][f][0];
+      red[warp][f][16 * mt + g][2 * t + 1] = acc[mt][f][1];
+      red[warp][f][16 * mt + g + 8][2 * t] = acc[mt][f][2];
+      red[warp][f][16 * mt + g + 8][2 * t + 1] = acc[mt][f][3];
+    }
   if (NORM) {
     // the eight warps' slices of K cover every element of rows 0..15 exactly once, so the row sums of squares
     // come from the very loads that fed the product: lanes of a quad, then warps, added in a fixed order
@@ -175,7 +202,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   }
   __syncthreads();
 
-  for (int idx = threadIdx.x; idx < 16 * NF * 8; idx += kSkinnyWarps * 32) {
+  for (int idx = threadIdx.x; idx < 16 * MT * NF * 8; idx += kSkinnyWarps * 32) {
     const int r = idx / (NF * 8), c = idx % (NF * 8);
     const int feat = n0 + c;
     if (r >= a.M || feat >= a.N) continue;
@@ -208,26 +235,40 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   }
 }
 
-template <int NF, bool NORM>
+template <int NF, bool NORM, int MT>
 static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
   const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
   const int threads = kSkinnyWarps * 32;
   switch (mode) {
-    case kStoreBf16: launch_prefetching(gemm_skinny_kernel<NF, kStoreBf16, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kStoreF32: launch_prefetching(gemm_skinny_kernel<NF, kStoreF32, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kAddF32: launch_prefetching(gemm_skinny_kernel<NF, kAddF32, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
-    default: launch_prefetching(gemm_skinny_kernel<NF, kSwiglu, NORM>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreBf16: launch_prefetching(gemm_skinny_kernel<NF, kStoreBf16, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreF32: launch_prefetching(gemm_skinny_kernel<NF, kStoreF32, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kAddF32: launch_prefetching(gemm_skinny_kernel<NF, kAddF32, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
+    default:
+      if constexpr (2 * NF * MT <= 8) {      // gate and up tiles of every row tile must fit the partial-sum buffer
+        launch_prefetching(gemm_skinny_kernel<NF, kSwiglu, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a);
+      } else {
+        return fail(1, "gemm_skinny: the gated epilogue is not built for %d features a block with %d rows", NF * 8, 16 * MT);
+      }
+      break;
   }
   return check_launch("gemm_skinny");
 }
 
 template <bool NORM>
 static int dispatch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
+  if (a.M > 32) {       // up to 64 rows: 8 or 16 features per block (the partial sums of 64 rows must fit shared memory)
+    if (mode == kSwiglu || a.N < 4096) return launch_skinny<1, false, 4>(a, mode, s);
+    return launch_skinny<2, false, 4>(a, mode, s);
+  }
+  if (a.M > 16) {
+    if (mode == kSwiglu || a.N < 4096) return launch_skinny<1, false, 2>(a, mode, s);
+    return launch_skinny<2, false, 2>(a, mode, s);
+  }
   // wide matrices: 16 or 32 features per block; narrow ones: 8, so that enough blocks exist to fill the GPU
-  if (mode == kSwiglu) return a.N >= 4096 ? launch_skinny<2, NORM>(a, mode, s) : launch_skinny<1, NORM>(a, mode, s);
-  if (a.N >= 32768) return launch_skinny<4, NORM>(a, mode, s);
-  if (a.N >= 4096) return launch_skinny<2, NORM>(a, mode, s);
-  return launch_skinny<1, NORM>(a, mode, s);
+  if (mode == kSwiglu) return a.N >= 4096 ? launch_skinny<2, NORM, 1>(a, mode, s) : launch_skinny<1, NORM, 1>(a, mode, s);
+  if (a.N >= 32768) return launch_skinny<4, NORM, 1>(a, mode, s);
+  if (a.N >= 4096) return launch_skinny<2, NORM, 1>(a, mode, s);
+  return launch_skinny<1, NORM, 1>(a, mode, s);
 }
 
 }  // namespace slb
@@ -236,14 +277,14 @@ using namespace slb;
 
 // 1 when the skinny kernel takes this problem (the caller otherwise uses the library product).
 extern "C" int slb_gemm_skinny_supported(int M, int N, int K) {
-  return M >= 1 && M <= 16 && K >= 32 && K % 32 == 0 && N >= 1;
+  return M >= 1 && M <= 64 && K >= 32 && K % 32 == 0 && N >= 1;
 }
 
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds 2 * N rows, C is [M, N]).
 extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
                                void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
-              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
+              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 64, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: X and W must be 16-byte aligned");
   SkinnyArgs a{};
@@ -255,8 +296,8 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
 // `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
 extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
                                     int K, int ldc, int mode, void* stream) {
-  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
-              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
+  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16,
+              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N && eps > 0.0f, "gemm_skinny: mode=%d ldc=%d N=%d eps=%g", mode, ldc, N, (double)eps);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)gain % 16 == 0),
               "gemm_skinny: X, gain and W must be 16-byte aligned");

@@ -1,13 +1,15 @@
 // bfloat16 matrix product on the fifth-generation tensor cores: C[M, N] = X[M, K] * W[N, K]^T for many rows (prefill).
 //
-// One block computes a 128 x BN tile of C (BN = 128 or 256 columns):
+// One block per SM walks over 128 x BN tiles of C (BN = 32 to 256 columns), with two accumulators in tensor memory
+// so that the epilogue of one tile overlaps the products of the next:
 //   * warp 0, one lane: the producer. For every 64-wide slice of K it asks TMA (cp.async.bulk.tensor) for the
 //     128 x 64 tile of X and the BN x 64 tile of W; both arrive in shared memory in the 128-byte-swizzled K-major
 //     layout that the tensor core reads, and their arrival is counted on the stage's "full" mbarrier.
 //   * warp 1, one lane: the MMA issuer. It waits for a full stage and issues four tcgen05.mma (K = 16 each,
 //     M = 128, N = BN) that accumulate into tensor memory (TMEM), then tcgen05.commit makes the stage's "empty"
-//     mbarrier fire when those MMAs have read the stage. After the last slice a commit arms the "done" mbarrier.
-//   * all four warps: the epilogue. Warp w reads rows 32w .. 32w+31 of the accumulator (tcgen05.ld, 32 columns at a
+//     mbarrier fire when those MMAs have read the stage. After a tile's last slice a commit arms the accumulator's
+//     "full" mbarrier; before reusing an accumulator it waits for the epilogue warps' "drained" arrivals.
+//   * warps 2 to 5: the epilogue. Each reads its 32 rows of the accumulator (tcgen05.ld, 32 columns at a
 //     time), applies the epilogue and stores: bfloat16, float32, float32 accumulate (residual stream), or the gated
 //     activation silu(gate) * up when W holds the gate rows followed by the up rows (sleuth/forge/model/mlp.py:37-40);
 //     the block then multiplies X by 128 gate rows and the 128 matching up rows in one N = 256 instruction.
@@ -26,7 +28,7 @@ namespace slb {
 constexpr int kTcBM = 128;
 constexpr int kTcBK = 64;             // bf16 elements per slice: 128 bytes, one swizzle row
 constexpr int kTcStages = 4;
-constexpr int kTcThreads = 128;
+constexpr int kTcThreads = 192;       // producer warp, MMA warp, four epilogue warps
 constexpr uint32_t kSpinLimit = 4000000u;
 
 enum TcMode : int { kTcBf16 = 0, kTcF32 = 1, kTcAddF32 = 2, kTcSwiglu = 3 };
@@ -105,6 +107,54 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ float fast_silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+// Stores 32 consecutive float32 accumulator values of one row according to the mode.
+__device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, const float (&v)[32]) {
+  const bool full = col0 + 32 <= a.N;
+  if (a.mode == kTcBf16 || a.mode == kTcSwiglu) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + col0;
+    if (full && (a.ldc % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 q;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        q.x = *reinterpret_cast<uint32_t*>(&p0); q.y = *reinterpret_cast<uint32_t*>(&p1);
+        q.z = *reinterpret_cast<uint32_t*>(&p2); q.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>(dst + j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < a.N) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(a.C) + (size_t)row * a.ldc + col0;
+    if (full && (a.ldc % 4 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (a.mode == kTcAddF32) {
+          const float4 o = *reinterpret_cast<const float4*>(dst + j);
+          q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
+        }
+        *reinterpret_cast<float4*>(dst + j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < a.N) dst[j] = (a.mode == kTcAddF32 ? dst[j] : 0.0f) + v[j];
+    }
+  }
+}
+
+// Persistent: a block walks the output tiles blockIdx.x, blockIdx.x + gridDim.x, ... Two accumulators in tensor
+// memory alternate, so the epilogue warps drain tile t while the tensor core already works on tile t + 1.
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
@@ -112,28 +162,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2, STAGE = A_BYTES + B_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcStages * STAGE);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 1);
-  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * kTcStages, done = empty0 + 8 * kTcStages;
+  constexpr int S = kTcStages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * STAGE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * S, tfull0 = empty0 + 8 * S, tempty0 = tfull0 + 16;
   const uint32_t tiles = smem_addr(smem);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kTcBM;
   const bool gated = a.mode == kTcSwiglu;
-  const int n0 = blockIdx.x * (gated ? BN / 2 : BN);      // first output column of this block
+  const int cols_per_tile = gated ? BN / 2 : BN;
+  const int m_tiles = (a.M + kTcBM - 1) / kTcBM, n_tiles = (a.N + cols_per_tile - 1) / cols_per_tile;
+  const int total = m_tiles * n_tiles;
   const int k_tiles = (a.K + kTcBK - 1) / kTcBK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull0 + 8 * i, 1);
+      mbar_init(tempty0 + 8 * i, 4);        // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {     // one warp allocates BN columns of tensor memory for the accumulator
+  if (warp == 2) {     // one warp allocates both accumulators: 2 * BN columns of tensor memory
     __syncwarp();
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -144,121 +199,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   pdl_launch_dependents();
   pdl_wait();          // X is the previous kernel's output
 
-  if (warp == 0 && lane == 0) {
-    // ---- producer ----
-    for (int kt = 0; kt < k_tiles; ++kt) {
-      const int s = kt % kTcStages;
-      if (kt >= kTcStages && !mbar_wait(empty0 + 8 * s, ((kt / kTcStages) - 1) & 1)) {
-        atomicExch(a.status, 1);
-        break;
-      }
-      const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
-      mbar_expect_tx(full0 + 8 * s, STAGE);
-      tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
-      if (gated) {
-        tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
-        tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
-      } else {
-        tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
-        if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer ----
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % S;
+          if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1)) {
+            atomicExch(a.status, 1);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
+          mbar_expect_tx(full0 + 8 * s, STAGE);
+          tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
+          tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
+          if (gated) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
+          else if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+        }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer ----
-    constexpr uint32_t idesc = instr_desc(kTcBM, BN);
-    bool ok = true;
-    for (int kt = 0; kt < k_tiles && ok; ++kt) {
-      const int s = kt % kTcStages;
-      if (!mbar_wait(full0 + 8 * s, (kt / kTcStages) & 1)) {
-        atomicExch(a.status, 2);
-        ok = false;
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      constexpr uint32_t idesc = instr_desc(kTcBM, BN);
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        if (t >= 2 && !mbar_wait(tempty0 + 8 * buf, ((t / 2) - 1) & 1)) {      // the epilogue has drained this accumulator
+          atomicExch(a.status, 4);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + (uint32_t)(buf * BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(full0 + 8 * s, (it / S) & 1)) {
+            atomicExch(a.status, 2);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
+          const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+#pragma unroll
+          for (int k4 = 0; k4 < kTcBK / 16; ++k4)    // 16 elements = 32 bytes further along K inside the swizzle row
+            mma_bf16_ss(acc, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+          mma_commit(empty0 + 8 * s);                // fires when these MMAs have read the stage
+        }
+        if (ok) mma_commit(tfull0 + 8 * buf);        // fires when the whole tile has been accumulated
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5, tensor-memory lanes 32 * (warp % 4) .. + 31 ----
+    const int quad = warp & 3;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      const int m0 = (tile % m_tiles) * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+      bool ready = true;
+      if (lane == 0) ready = mbar_wait(tfull0 + 8 * buf, (t / 2) & 1);
+      ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+      if (!ready) {
+        if (lane == 0) atomicExch(a.status, 3);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
-      const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+      for (int c = 0; c < cols_per_tile; c += 32) {
+        uint32_t r[32];
+        float v[32];
+        tmem_ld32(lane_base + c, r);
+        if (gated) {
+          uint32_t u[32];
+          tmem_ld32(lane_base + BN / 2 + c, u);
 #pragma unroll
-      for (int k4 = 0; k4 < kTcBK / 16; ++k4)      // 16 elements = 32 bytes further along K inside the swizzle row
-        mma_bf16_ss(tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
-      mma_commit(empty0 + 8 * s);                  // fires when these MMAs have read the stage
-    }
-    mma_commit(done);                              // fires when every MMA issued so far has completed
-  }
-
-  // ---- epilogue: all four warps ----
-  __syncwarp();
-  bool ready = true;
-  if (lane == 0) ready = mbar_wait(done, 0);
-  ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-  if (!ready && lane == 0) atomicExch(a.status, 3);
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (ready) {
-    const int row = m0 + warp * 32 + lane;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    const int out_cols = gated ? BN / 2 : BN;
-    for (int c = 0; c < out_cols; c += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + c, r);
-      if (gated) {
-        uint32_t u[32];
-        tmem_ld32(lane_base + BN / 2 + c, u);
-        if (row < a.M) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + n0 + c;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (n0 + c + j < a.N) {
-              const float g = __uint_as_float(r[j]);
-              dst[j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * __uint_as_float(u[j]));
-            }
-          }
-        }
-      } else if (row < a.M) {
-        const bool full = n0 + c + 32 <= a.N;
-        if (a.mode == kTcBf16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + n0 + c;
-          if (full && (a.ldc % 8 == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v;
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-              v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-              v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-              *reinterpret_cast<uint4*>(dst + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + c + j < a.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-          }
+          for (int j = 0; j < 32; ++j) v[j] = fast_silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
         } else {
-          float* dst = reinterpret_cast<float*>(a.C) + (size_t)row * a.ldc + n0 + c;
-          if (full && (a.ldc % 4 == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                     __uint_as_float(r[j + 3]));
-              if (a.mode == kTcAddF32) {
-                const float4 o = *reinterpret_cast<const float4*>(dst + j);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *reinterpret_cast<float4*>(dst + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + c + j < a.N) dst[j] = (a.mode == kTcAddF32 ? dst[j] : 0.0f) + __uint_as_float(r[j]);
-          }
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         }
+        if (row < a.M && n0 + c < a.N) store_row32(a, row, n0 + c, v);
       }
+      // this warp has read its part of the accumulator: let the tensor core have the buffer back
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+  if (warp == 2)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
 }
 
 // ------------------------------------------------------------------------------------ host side ----
@@ -295,15 +332,22 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 template <int BN>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s) {
-  const int smem = kTcStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kTcStages + 1) * 8 + 16 + 1024;
+  const int smem = kTcStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kTcStages + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(2, "gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  const int cols_per_block = a.mode == kTcSwiglu ? BN / 2 : BN;
-  dim3 grid((a.N + cols_per_block - 1) / cols_per_block, (a.M + kTcBM - 1) / kTcBM);
+  const int cols_per_tile = a.mode == kTcSwiglu ? BN / 2 : BN;
+  const long long total = (long long)((a.N + cols_per_tile - 1) / cols_per_tile) * ((a.M + kTcBM - 1) / kTcBM);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  dim3 grid((unsigned)(total < sms ? total : sms));
   launch_prefetching(gemm_tc_kernel<BN>, grid, dim3(kTcThreads), (size_t)smem, s, mx, mw, a);
   return check_launch("gemm_tc");
 }
@@ -324,15 +368,23 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0),
               "gemm_tc: X, W and C must be 16-byte aligned");
   const bool gated = mode == kTcSwiglu;
-  // 256 columns per block when the matrix is wide enough to fill the GPU that way, else 128
-  const bool wide = gated || ((long long)((M + 127) / 128) * ((N + 255) / 256) >= 120);
+  // The widest tile that still gives the GPU about a hundred tiles to work on: wide tiles reuse the X tile for more
+  // columns, narrow ones keep every SM streaming weights when there are few rows.
+  const long long m_tiles = (M + 127) / 128;
+  int bn = 256;
+  while (bn > (gated ? 64 : 32) && m_tiles * ((N + (gated ? bn / 2 : bn) - 1) / (gated ? bn / 2 : bn)) < 100) bn >>= 1;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, kTcBM);
   if (rc) return rc;
-  rc = make_map(&mw, W, gated ? 2ll * N : N, K, 128);
+  rc = make_map(&mw, W, gated ? 2ll * N : N, K, gated ? bn / 2 : (bn < 128 ? bn : 128));
   if (rc) return rc;
   TcArgs a;
   a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.mode = mode; a.up_row0 = N; a.status = status;
   cudaStream_t s = (cudaStream_t)stream;
-  return wide ? launch_tc<256>(mx, mw, a, s) : launch_tc<128>(mx, mw, a, s);
+  switch (bn) {
+    case 256: return launch_tc<256>(mx, mw, a, s);
+    case 128: return launch_tc<128>(mx, mw, a, s);
+    case 64: return launch_tc<64>(mx, mw, a, s);
+    default: return launch_tc<32>(mx, mw, a, s);
+  }
 }

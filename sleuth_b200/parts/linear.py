@@ -68,7 +68,7 @@ class Linear:
         M = h.shape[0]
         if isinstance(h, Normed):
             if (self.dtype == torch.bfloat16 and h.gain is not None and into is None
-                    and ops.skinny_supported(M, self.out_features, self.in_features)):
+                    and ops.skinny_supported(M, self.out_features, self.in_features, norm=True)):
                 want = out_dtype or (out.dtype if out is not None else self.dtype)
                 if out is None:
                     out = ws.take((M, self.out_features), want)

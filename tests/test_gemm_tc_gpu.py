@@ -56,3 +56,9 @@ def test_refusals():
     x = torch.zeros(32, 20, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(RuntimeError, match="multiple of 8"):
         o.gemm_tc(x, torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV), torch.zeros(32, 8, dtype=torch.bfloat16, device=DEV), "bf16")
+
+
+@pytest.mark.parametrize("M,N,K,mode", [(64, 4096, 1024, "bf16"), (64, 1024, 3072, "add"), (40, 3072, 1024, "swiglu"),
+                                         (17, 1024, 2048, "add"), (100, 151936, 64, "f32"), (33, 96, 64, "swiglu")])
+def test_gemm_tc_few_rows_take_narrow_tiles(M, N, K, mode):
+    run(M, N, K, mode)

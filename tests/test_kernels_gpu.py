@@ -268,7 +268,7 @@ def test_qkv_post(dtype, heads, kv_heads, hd, rot):
 
 # ------------------------------------------------------------------ few-rows product ----
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 40, 64])
 @pytest.mark.parametrize("N,K", [(1024, 1024), (1000, 2048), (4096, 1024), (40, 96), (33000, 64), (1024, 3072)])
 def test_gemm_skinny(M, N, K):
     o = ops()
@@ -292,7 +292,7 @@ def test_gemm_skinny(M, N, K):
     assert torch.equal(acc, again)
 
 
-@pytest.mark.parametrize("M,inter,K", [(1, 3072, 1024), (8, 200, 64), (16, 4100, 128), (5, 136, 96)])
+@pytest.mark.parametrize("M,inter,K", [(1, 3072, 1024), (8, 200, 64), (16, 4100, 128), (5, 136, 96), (24, 3072, 1024), (64, 200, 64)])
 def test_gemm_skinny_gated_activation(M, inter, K):
     o = ops()
     g = torch.Generator().manual_seed(inter)
@@ -306,7 +306,7 @@ def test_gemm_skinny_gated_activation(M, inter, K):
 
 def test_gemm_skinny_refuses_what_it_cannot_run():
     o = ops()
-    assert not o.skinny_supported(17, 64, 64) and not o.skinny_supported(4, 64, 40)
+    assert not o.skinny_supported(65, 64, 64) and not o.skinny_supported(4, 64, 40)
     x = torch.zeros(4, 40, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(RuntimeError, match="multiple of 32"):
         o.gemm_skinny(x, torch.zeros(8, 40, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV), "bf16")
