@@ -40,14 +40,13 @@ class GatedMLP(Part):
         T = h.shape[0]
         mark = ws.mark()
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
-        if self.ctx.dtype == torch.bfloat16 and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden):
+        if self.ctx.dtype == torch.bfloat16 and linear.use_skinny(T, self.spec.intermediate, self.spec.hidden):
             # norm in the product's prologue (when handed the stream), activation in its epilogue
             if isinstance(h, Normed) and h.gain is not None and FUSE_NORM:
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream)
             else:
                 ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
-        elif (self.ctx.dtype == torch.bfloat16 and linear.USE_TC
-              and ops.tc_supported(T, self.spec.intermediate, self.spec.hidden)):
+        elif self.ctx.dtype == torch.bfloat16 and linear.use_tc(T, self.spec.intermediate, self.spec.hidden):
             ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)

@@ -23,9 +23,24 @@ from .base import Normed
 
 import os
 
-# SLEUTH_B200_GEMM=library sends the many-row bfloat16 products to cuBLAS instead of this package's tcgen05 kernel
-# (for comparison; K that is no multiple of 8 goes there in any case).
-USE_TC = os.environ.get("SLEUTH_B200_GEMM", "own") != "library"
+# Which kernel multiplies how many rows (bfloat16), as measured on a B200 with the Qwen3-0.6B shapes:
+#   up to SKINNY_ROWS rows   the weight-streaming kernel (equal to the library at 32 rows, behind it at 64)
+#   from TC_ROWS rows on     this package's tcgen05 kernel (level with the library at 2,048 rows, ahead with the
+#                            gated epilogue, behind it for a few hundred rows, where its 128-row tiles are few)
+#   between                  the library product (cuBLAS through torch.mm)
+# SLEUTH_B200_GEMM=own sends everything the own kernels take to them, =library everything above SKINNY_ROWS to cuBLAS.
+_CHOICE = os.environ.get("SLEUTH_B200_GEMM", "auto")
+USE_TC = _CHOICE != "library"
+SKINNY_ROWS = 64 if _CHOICE == "own" else 32
+TC_ROWS = 1 if _CHOICE == "own" else 1024
+
+
+def use_skinny(M: int, N: int, K: int, norm: bool = False) -> bool:
+    return M <= SKINNY_ROWS and ops.skinny_supported(M, N, K, norm)
+
+
+def use_tc(M: int, N: int, K: int) -> bool:
+    return USE_TC and M >= TC_ROWS and ops.tc_supported(M, N, K)
 
 _MODE: dict = {}
 
@@ -68,7 +83,7 @@ class Linear:
         M = h.shape[0]
         if isinstance(h, Normed):
             if (self.dtype == torch.bfloat16 and h.gain is not None and into is None
-                    and ops.skinny_supported(M, self.out_features, self.in_features, norm=True)):
+                    and use_skinny(M, self.out_features, self.in_features, norm=True)):
                 want = out_dtype or (out.dtype if out is not None else self.dtype)
                 if out is None:
                     out = ws.take((M, self.out_features), want)
@@ -84,7 +99,7 @@ class Linear:
                 out = ws.take((M, self.out_features), torch.float32)
             ops.gemm_f32(h, self.weight, out, stream=stream)
             return out
-        if ops.skinny_supported(M, self.out_features, self.in_features):
+        if use_skinny(M, self.out_features, self.in_features):
             if into is not None:
                 ops.gemm_skinny(h, self.weight, into, "add", stream)
                 return into
@@ -93,7 +108,7 @@ class Linear:
                 out = ws.take((M, self.out_features), want)
             ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream)
             return out
-        if USE_TC and ops.tc_supported(M, self.out_features, self.in_features):
+        if use_tc(M, self.out_features, self.in_features):
             if into is not None:
                 ops.gemm_tc(h, self.weight, into, "add", stream)
                 return into

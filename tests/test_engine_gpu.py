@@ -266,3 +266,27 @@ def test_missing_weights_are_reported_at_load(model_folders, tmp_path):
     write_safetensors(t, d / "model.safetensors")
     with pytest.raises(WeightError, match="missing.*gate_proj"):
         sb.load(d, dtype="fp32")
+
+
+@pytest.mark.parametrize("rows", ["tensor-memory kernel for every product", "weight-streaming kernel up to 64 rows"])
+def test_bfloat16_engine_on_each_own_product_kernel(rows, model_folders, monkeypatch):
+    """The engine picks its product kernel by row count; here each own kernel is made to serve every product it
+    can take, prompts and single tokens alike, and the logits must still match the plain implementation."""
+    from sleuth_b200.parts import linear
+    if rows.startswith("tensor"):
+        monkeypatch.setattr(linear, "SKINNY_ROWS", 0)
+        monkeypatch.setattr(linear, "TC_ROWS", 1)
+    else:
+        monkeypatch.setattr(linear, "SKINNY_ROWS", 64)
+    monkeypatch.setenv("SLEUTH_B200_CHECK", "1")
+    for name in ("C", "D"):
+        eng, ref = load(model_folders[name], "bf16", use_graphs=False), oracle(model_folders[name], "bf16")
+        reqs = requests_for(name, [150, 40, 9], seed=6)
+        slots = eng.open(3)
+        out = eng.step([(s, ids[:-1], (len(ids) - 2,)) for s, ids in zip(slots, reqs)]).cpu()
+        torch.testing.assert_close(out, torch.stack([ref(ids)[-2] for ids in reqs]), **TOL["bf16"])
+        out = eng.step([(s, ids[-1:], (0,)) for s, ids in zip(slots, reqs)]).cpu()
+        torch.testing.assert_close(out, torch.stack([ref(ids)[-1] for ids in reqs]), **TOL["bf16"])
+        eng.close(slots)
+        from sleuth_b200.kernels import ops
+        ops.gemm_tc_check("cuda:0")
