@@ -43,6 +43,15 @@ struct FlashArgs {
   float* part_o;                // [n, H, splits, HD] unnormalised
   float* part_ml;               // [n, H, splits, 2]  running max (log2 units) and sum
   int* counters;                // [n, kv_heads, row_tiles] zero between launches: slices that have finished
+  // decode with the q/k/v post-processing fused in (qkv != null): q is not read; instead the raw projection rows
+  const __nv_bfloat16* qkv;     // [n, (H + 2 * qkv_kv_heads) * HD]
+  const float* bias;            // [(H + 2 * qkv_kv_heads) * HD] or null
+  const float* q_gain;          // [HD] or null
+  const float* k_gain;
+  const float* cos_table;       // [positions, HD / 2] or null: the whole head is rotated, or nothing
+  const float* sin_table;
+  float eps;
+  int qkv_kv_heads;             // key/value heads present in qkv (0: this layer reads another layer's cache)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -287,12 +296,66 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
 // keeps the memory system busy when a block's work per page is short compared with the latency of a load.
 constexpr int kDecodeStages = 3;
 
+// One row of the raw q/k/v projection, as csrc/qkv_post.cu treats it: + bias, RMSNorm over the head with `gain`
+// (when given), rotation of the whole head by the token's angles (when tables are given); float32 throughout.
+// Lane l gets channels l * EPL .. l * EPL + EPL - 1; the whole warp must call.
+template <int HD>
+__device__ __forceinline__ void post_row(const __nv_bfloat16* src, const float* bias, const float* gain, float eps,
+                                         const float* cs, const float* sn, int lane, float (&v)[HD / 32]) {
+  constexpr int EPL = HD / 32;
+  const int c0 = lane * EPL;
+  float ss = 0.0f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    float x = __bfloat162float(src[c0 + e]);
+    if (bias) x += bias[c0 + e];
+    v[e] = x;
+    ss = fmaf(x, x, ss);
+  }
+  if (gain) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = (v[e] * inv) * gain[c0 + e];
+  }
+  if (cs) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float partner = __shfl_xor_sync(0xffffffffu, v[e], 16);
+      const float other = lane < 16 ? -partner : partner;
+      v[e] = v[e] * cs[(lane & 15) * EPL + e] + other * sn[(lane & 15) * EPL + e];
+    }
+  }
+}
+
+// Writes a lane's EPL channels of `row` into a swizzled [rows][HD] bfloat16 tile in shared memory.
+template <int HD>
+__device__ __forceinline__ void put_row(unsigned char* tile, int row, int lane, const float (&v)[HD / 32]) {
+  constexpr int EPL = HD / 32;
+  const int c0 = lane * EPL;
+  unsigned char* dst = tile + swz<HD>(row, c0 & ~7) + (c0 & 7) * 2;
+  if constexpr (EPL == 4) {
+    uint2 pk;
+    pk.x = pack_bf16(v[0], v[1]);
+    pk.y = pack_bf16(v[2], v[3]);
+    *reinterpret_cast<uint2*>(dst) = pk;
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v[0], v[1]);
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
-  pdl_enter();
+  // Fused form: the keys and values of earlier tokens, the block table and the lengths were all written before the
+  // kernel that precedes this one began, so pages are requested before the wait for that kernel (which produces
+  // only the raw projection of the new token). Unfused form: the preceding kernel writes the newest cache row.
+  const bool fused = a.qkv != nullptr;
+  pdl_launch_dependents();
+  if (!fused) pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;
   constexpr int S = kDecodeStages;
+  constexpr int EPL = HD / 32;
   const uint32_t sK = smem_u32(smem), sV = sK + S * TILE;
   const uint32_t sQ = sV + S * TILE;          // [16][HD]
   unsigned char* sQ_ptr = smem + 2 * S * TILE;
@@ -324,25 +387,68 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
 
-  if (my_lo <= my_hi) {
-    auto fetch = [&](int page) {      // one commit group per page, empty beyond the slice
-      if (page <= my_hi) {
-        const int st = (page - my_lo) % S;
-        const size_t base = ((size_t)page_of(page) * a.kv_heads + kh) * 64 * HD;
-        load_page<HD, kFlashThreads>(smem, st * TILE, a.k_pool + base, pos + 1 - page * 64, tid);
-        load_page<HD, kFlashThreads>(smem, (S + st) * TILE, a.v_pool + base, pos + 1 - page * 64, tid);
-      }
-      cp_async_commit();
-    };
-    for (int i = tid; i < 16 * (HD / 8); i += kFlashThreads) {
-      const int row = i / (HD / 8), ch = i % (HD / 8);
-      if (row < rows)
-        cp_async16(sQ + swz<HD>(row, ch * 8), a.q + ((size_t)tok * a.heads + head0 + row) * HD + ch * 8);
-      else
-        *reinterpret_cast<uint4*>(sQ_ptr + swz<HD>(row, ch * 8)) = make_uint4(0, 0, 0, 0);
+  auto fetch = [&](int page) {      // one commit group per page, empty beyond the slice
+    if (page <= my_hi) {
+      const int st = (page - my_lo) % S;
+      const size_t base = ((size_t)page_of(page) * a.kv_heads + kh) * 64 * HD;
+      load_page<HD, kFlashThreads>(smem, st * TILE, a.k_pool + base, pos + 1 - page * 64, tid);
+      load_page<HD, kFlashThreads>(smem, (S + st) * TILE, a.v_pool + base, pos + 1 - page * 64, tid);
     }
-    fetch(my_lo);            // group 0 also carries the queries
+    cp_async_commit();
+  };
+  if (my_lo <= my_hi) {
+    fetch(my_lo);
     fetch(my_lo + 1);
+  }
+  // Nothing but read-only loads may come before this wait: the workspace this kernel writes to is shared with
+  // kernels that may still be running.
+  if (fused) pdl_wait();
+  if (my_lo <= my_hi) {
+    // the newest token's own key and value are not in the cache yet in the fused form: the block whose slice
+    // holds the last page works them out itself (warp 0 the key, warp 1 the value) and patches its copy of the page
+    const bool owns_last = fused && a.qkv_kv_heads > 0 && my_hi == page_hi;
+    float new_kv[EPL];
+    if (fused) {
+      const int rows_per_token = a.heads + 2 * a.qkv_kv_heads;
+      const __nv_bfloat16* raw = a.qkv + (size_t)tok * rows_per_token * HD;
+      const float* cs = a.cos_table ? a.cos_table + (size_t)pos * (HD / 2) : nullptr;
+      const float* sn = a.cos_table ? a.sin_table + (size_t)pos * (HD / 2) : nullptr;
+      for (int row = warp; row < 16; row += kFlashThreads / 32) {
+        float v[EPL];
+        if (row < rows) {
+          const int head = head0 + row;
+          post_row<HD>(raw + (size_t)head * HD, a.bias ? a.bias + (size_t)head * HD : nullptr, a.q_gain, a.eps, cs, sn, lane, v);
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) v[e] = 0.0f;
+        }
+        put_row<HD>(sQ_ptr, row, lane, v);
+      }
+      if (owns_last && warp < 2) {
+        const int r = a.heads + (warp == 0 ? 0 : a.qkv_kv_heads) + kh;
+        post_row<HD>(raw + (size_t)r * HD, a.bias ? a.bias + (size_t)r * HD : nullptr, warp == 0 ? a.k_gain : nullptr, a.eps,
+                     warp == 0 ? cs : nullptr, sn, lane, new_kv);
+        if (rt == 0) {      // one block per (sequence, kv head) stores the row for later steps
+          __nv_bfloat16* pool = warp == 0 ? const_cast<__nv_bfloat16*>(a.k_pool) : const_cast<__nv_bfloat16*>(a.v_pool);
+          __nv_bfloat16* dst = pool + (((size_t)page_of(page_hi) * a.kv_heads + kh) * 64 + (pos % 64)) * HD + lane * EPL;
+          if constexpr (EPL == 4) {
+            uint2 pk;
+            pk.x = pack_bf16(new_kv[0], new_kv[1]);
+            pk.y = pack_bf16(new_kv[2], new_kv[3]);
+            *reinterpret_cast<uint2*>(dst) = pk;
+          } else {
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16(new_kv[0], new_kv[1]);
+          }
+        }
+      }
+    } else {
+      for (int i = tid; i < 16 * (HD / 8); i += kFlashThreads) {
+        const int row = i / (HD / 8), ch = i % (HD / 8);
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < rows) val = *reinterpret_cast<const uint4*>(a.q + ((size_t)tok * a.heads + head0 + row) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(sQ_ptr + swz<HD>(row, ch * 8)) = val;
+      }
+    }
     uint32_t qf[HD / 16][4];
 
     for (int page = my_lo; page <= my_hi; ++page) {
@@ -350,6 +456,10 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       fetch(page + 2);       // into the buffer that the page before this one has left
       cp_async_wait<2>();    // all but the two newest groups: this page has landed
       __syncthreads();
+      if (owns_last && page == page_hi) {     // put the new token's key and value where the cache copy has a stale row
+        if (warp < 2) put_row<HD>(smem + ((warp == 0 ? 0 : S) + stage) * TILE, pos % 64, lane, new_kv);
+        __syncthreads();
+      }
       if (page == my_lo) {
 #pragma unroll
         for (int kb = 0; kb < HD / 16; ++kb) {
@@ -547,7 +657,10 @@ static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
     configured = true;
   }
   dim3 grid(a.splits * row_tiles, a.kv_heads, n_seqs);
-  launch(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
+  if (a.qkv != nullptr)      // the fused form asks for its pages before it waits for the kernel in front of it
+    launch_prefetching(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
+  else
+    launch(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
   return check_launch("attention (decode)");
 }
 
@@ -587,7 +700,18 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
                                     const int* seq_start, const int* past, const int* block_table, int table_stride,
                                     int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
                                     int splits, float* scratch, long long scratch_floats, int* counters,
-                                    long long n_counters, void* stream) {
+                                    long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
+                                    const float* q_gain, const float* k_gain, const float* cos_table,
+                                    const float* sin_table, float eps, void* stream) {
+  // qkv != null: `q` is ignored; the kernel takes the new token's raw projection rows [n, (H + 2 * qkv_kv_heads) * hd],
+  // applies bias, QK-norm and the rotation itself, and (qkv_kv_heads == kv_heads) writes the token's key and value
+  // into the cache. cos/sin tables, if given, are [positions, hd / 2]: the whole head rotates.
+  SLB_REQUIRE(qkv != nullptr || q != nullptr, "attention (decode): neither q nor the raw projection was given");
+  SLB_REQUIRE(qkv == nullptr || qkv_kv_heads == 0 || qkv_kv_heads == kv_heads,
+              "attention (decode): the raw projection holds %d key/value heads, the cache %d", qkv_kv_heads, kv_heads);
+  SLB_REQUIRE(qkv == nullptr || ((q_gain == nullptr) == (k_gain == nullptr)) || qkv_kv_heads == 0,
+              "attention (decode): q and k gains go together");
+  SLB_REQUIRE(qkv == nullptr || (cos_table == nullptr) == (sin_table == nullptr), "attention (decode): cos and sin tables go together");
   SLB_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention (decode): seqs=%d heads=%d kv_heads=%d", n_seqs, heads, kv_heads);
   SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (decode): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
@@ -607,6 +731,8 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = splits;
   a.part_o = scratch;
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
+  a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
+  a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps;
   return head_dim == 64 ? launch_decode<64>(a, n_seqs, (cudaStream_t)stream)
                         : launch_decode<128>(a, n_seqs, (cudaStream_t)stream);
 }

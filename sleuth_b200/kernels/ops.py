@@ -156,19 +156,32 @@ def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_tab
 
 
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
-                     window: int, scale: float, splits: int, scratch, stream=None) -> None:
-    """Tensor-core attention for a step in which every sequence brings one token (split-KV)."""
-    _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch)
+                     window: int, scale: float, splits: int, scratch, stream=None, qkv=None, qkv_kv_heads: int = 0,
+                     bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6) -> None:
+    """Tensor-core attention for a step in which every sequence brings one token (split-KV).
+
+    With ``qkv`` (the raw fused projection ``[n, (heads + 2 * qkv_kv_heads) * head_dim]``) the kernel also does what
+    ``qkv_post`` does for that token: bias, per-head QK-norm, rotation of the whole head, and, when
+    ``qkv_kv_heads == kv_heads``, the write of its key and value into the cache; ``q`` is then not read."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch, qkv, bias, q_gain, k_gain, cos, sin)
     n = block_table.shape[0]
-    _need(q.shape == (n, heads, head_dim) and out.shape == (n, heads * head_dim), "attention: shapes disagree")
-    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
+    _need(out.shape == (n, heads * head_dim) and out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16,
+          "attention (tensor cores): shapes disagree or not bfloat16")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(scratch is None or scratch.dtype == torch.float32, "attention: scratch is float32")
-    counters = _decode_counters(q.device, n * kv_heads * ((heads // kv_heads + 15) // 16)) if splits > 1 else None
+    if qkv is None:
+        _need(q is not None and q.shape == (n, heads, head_dim) and q.dtype == torch.bfloat16, "attention: q shape or dtype")
+    else:
+        _need(qkv.shape == (n, (heads + 2 * qkv_kv_heads) * head_dim) and qkv.dtype == torch.bfloat16, "attention: raw projection shape")
+        for v in (bias, q_gain, k_gain, cos, sin):
+            _need(v is None or v.dtype == torch.float32, "attention: gains, biases and tables are float32")
+        _need(cos is None or (cos.shape[1] == head_dim // 2 and sin.shape == cos.shape), "attention: rotation tables")
+    counters = _decode_counters(out.device, n * kv_heads * ((heads // kv_heads + 15) // 16)) if splits > 1 else None
     lib().call("slb_attention_decode", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
                _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
                int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
-               0 if counters is None else counters.numel(), stream if stream is not None else current_stream())
+               0 if counters is None else counters.numel(), _p(qkv), int(qkv_kv_heads), _p(bias), _p(q_gain), _p(k_gain),
+               _p(cos), _p(sin), float(eps), stream if stream is not None else current_stream())
 
 
 _COUNTERS: dict = {}

@@ -82,15 +82,28 @@ class GQAAttention(Part):
         table = b.tables[view.group]
         mark = ws.mark()
         qkv = self.qkv.forward(h, ws=ws, stream=b.stream)
-        q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
         tables = self.position.tables()
         cos, sin = tables if tables is not None else (None, None)
+        rot = self.position.rot_dim
+        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
+        if flash and b.max_count == 1 and rot in (0, s.head_dim) and (writes or s.reads_shared_kv):
+            # one token per sequence: the attention kernel post-processes q/k/v itself and appends to the cache
+            splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
+            floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
+            scratch = ws.take((floats,), torch.float32) if floats else None
+            ops.attention_decode(None, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
+                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream, qkv=qkv,
+                                 qkv_kv_heads=kvh, bias=self.bias, q_gain=self.q_gain, k_gain=self.k_gain,
+                                 cos=cos if rot else None, sin=sin if rot else None, eps=s.qk_norm_eps)
+            self.o.forward(y, into=x, ws=ws, stream=b.stream)
+            ws.release(mark)
+            return
+        q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
         ops.qkv_post(qkv, self.bias, self.q_gain, self.k_gain, cos, sin, q,
                      view.k_pool if writes else None, view.v_pool if writes else None,
-                     b.tok_seq, b.tok_pos, table, s.heads, kvh, s.head_dim, self.position.rot_dim,
-                     s.qk_norm_eps, b.stream)
-        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
-        if not ops.flash_supported(s.head_dim, self.ctx.dtype):
+                     b.tok_seq, b.tok_pos, table, s.heads, kvh, s.head_dim, rot, s.qk_norm_eps, b.stream)
+        if not flash:
             ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
                           s.head_dim, view.window, self.scale, b.stream)
         elif b.max_count == 1:

@@ -353,3 +353,61 @@ def test_gemm_skinny_with_the_norm_fused_in(M, N, K, mode):
     o.gemm_skinny_norm(x.to(DEV), gain.to(DEV), eps, w.to(DEV), out, mode)
     tl = dict(rtol=2e-2, atol=2e-2) if dt == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(out.cpu().double(), ref, **tl)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,splits,bias,rot", [(4, 2, 128, 1, False, True), (16, 8, 128, 5, False, True),
+                                                                 (5, 1, 64, 3, True, True), (40, 2, 64, 2, True, False)])
+def test_attention_decode_with_qkv_post_fused(heads, kv_heads, hd, splits, bias, rot):
+    """The decode kernel given the raw projection of the new token: it must normalise, rotate, append to the
+    cache and attend exactly as qkv_post followed by attention do."""
+    o = ops()
+    bf = torch.bfloat16
+    gen = torch.Generator().manual_seed(heads * hd + splits)
+    pasts = [0, 63, 64, 300, 1000]
+    n = len(pasts)
+    lens = [p + 1 for p in pasts]
+    k_pool, v_pool, table, ks, vs = make_cache(lens, kv_heads, hd, bf, gen)
+    rows = heads + 2 * kv_heads
+    qkv = torch.randn(n, rows * hd, generator=gen).to(bf)
+    b = (torch.randn(rows * hd, generator=gen) * 0.1) if bias else None
+    qg, kg = 1 + 0.1 * torch.randn(hd, generator=gen), 1 + 0.1 * torch.randn(hd, generator=gen)
+    eps, theta = 1e-5, 1e4
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    ang = torch.outer(torch.arange(1100, dtype=torch.float32), inv)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    x = qkv.double().view(n, rows, hd) + (b.double().view(rows, hd) if bias else 0)
+
+    def norm(v, gain):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * gain.double()
+
+    def rope(v):
+        if not rot:
+            return v
+        c, s = cos[pasts].double()[:, None, :], sin[pasts].double()[:, None, :]
+        a, bb = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([a * c - bb * s, bb * c + a * s], dim=-1)
+
+    q_ref = rope(norm(x[:, :heads], qg))
+    k_new = rope(norm(x[:, heads:heads + kv_heads], kg)).to(bf)           # what the cache will hold
+    v_new = x[:, heads + kv_heads:].to(bf)
+    scale = 1.0 / math.sqrt(hd)
+    ref = []
+    for i in range(n):
+        kk = torch.cat([ks[i][:pasts[i]].float(), k_new[i:i + 1].float()])
+        vv = torch.cat([vs[i][:pasts[i]].float(), v_new[i:i + 1].float()])
+        ref.append(plain_attention(q_ref[i:i + 1].to(bf).float(), kk, vv, [pasts[i]], 0, scale))
+    ref = torch.cat(ref)
+    d = lambda a: None if a is None else torch.as_tensor(a).to(DEV)
+    kp, vp = d(k_pool), d(v_pool)                 # the newest row of every sequence is still random rubbish here
+    out = torch.full((n, heads * hd), float("nan")).to(bf).to(DEV)
+    floats = o.decode_scratch_floats(n, heads, hd, splits)
+    scratch = torch.full((max(floats, 1),), float("nan"), device=DEV)
+    starts = np.arange(n + 1, dtype=np.int32)
+    o.attention_decode(None, kp, vp, out, d(starts), d(np.asarray(pasts, dtype=np.int32)), d(table), heads, kv_heads, hd,
+                       0, scale, splits, scratch if floats else None, qkv=d(qkv), qkv_kv_heads=kv_heads, bias=d(b),
+                       q_gain=d(qg), k_gain=d(kg), cos=d(cos) if rot else None, sin=d(sin) if rot else None, eps=eps)
+    torch.testing.assert_close(out.cpu().double().view(n, heads, hd), ref, rtol=2e-2, atol=1.5e-2)
+    for i in range(n):
+        page = int(table[i, pasts[i] // 64])
+        torch.testing.assert_close(kp[page, :, pasts[i] % 64].cpu().float(), k_new[i].float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(vp[page, :, pasts[i] % 64].cpu().float(), v_new[i].float(), rtol=2e-2, atol=2e-2)
