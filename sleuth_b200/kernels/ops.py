@@ -155,6 +155,31 @@ def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_tab
                float(scale), stream if stream is not None else current_stream())
 
 
+def attention_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tcgen05 attention kernel takes this shape (bfloat16, head size 64 or 128, group size dividing 128)."""
+    if dtype != torch.bfloat16 or heads <= 0 or kv_heads <= 0 or heads % kv_heads:
+        return False
+    group = heads // kv_heads
+    return head_dim in (64, 128) and group <= 128 and 128 % group == 0
+
+
+def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
+                 kv_heads: int, head_dim: int, window: int, scale: float, stream=None) -> None:
+    """Attention for a step in which sequences bring many tokens, on the tcgen05 tensor cores (same contract as
+    ``attention_prefill``). A bounded wait that gave up inside the kernel shows in ``tc_check``."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    T, n = q.shape[0], block_table.shape[0]
+    _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
+    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tcgen05): bfloat16 only")
+    _need(q.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous(),
+          "attention (tcgen05): contiguous tensors")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
+    _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
+    lib().call("slb_attention_tc", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
+               _p(block_table), block_table.shape[1], n, int(max_count), T, k_pool.shape[0], heads, kv_heads, head_dim,
+               int(window), float(scale), _p(_tc_status(q.device)), stream if stream is not None else current_stream())
+
+
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
                      window: int, scale: float, splits: int, scratch, stream=None, qkv=None, qkv_kv_heads: int = 0,
                      bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6) -> None:
@@ -289,8 +314,9 @@ def gemm_tc_check(device) -> None:
     code = int(st.item())
     if code:
         st.zero_()
-        raise RuntimeError(f"gemm_tc: a wait inside the kernel gave up (code {code}: 1 = free stage, 2 = loaded "
-                           f"stage, 3 = finished accumulator); its results are not valid")
+        raise RuntimeError(f"a wait inside a tcgen05 kernel gave up (code {code}; product: 1 = free stage, 2 = loaded "
+                           f"stage, 3 = finished accumulator, 4 = drained accumulator; attention: 20 = shared memory "
+                           f"misaligned, 21-27 = producer and MMA waits, 28-32 = softmax waits); its results are not valid")
 
 
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:

@@ -14,6 +14,7 @@ application wrote.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -22,6 +23,18 @@ from ..kernels import ops
 from .base import BuildContext, ParamDecl, Part, build_position, register_mixer
 from .linear import Linear
 from .spec import AttentionSpec
+
+
+# Which kernel serves a step that brings several tokens per sequence: "auto" takes the tcgen05 kernel once a
+# sequence fills at least one of its 128-row tiles, "mma" always the mma.sync kernel, "tc" the tcgen05 kernel
+# whenever it takes the shape.
+ATTENTION_CHOICE = os.environ.get("SLEUTH_B200_ATTENTION", "auto")
+
+
+def use_tc_attention(heads: int, kv_heads: int, head_dim: int, dtype, max_count: int) -> bool:
+    if ATTENTION_CHOICE == "mma" or not ops.attention_tc_supported(heads, kv_heads, head_dim, dtype):
+        return False
+    return ATTENTION_CHOICE == "tc" or max_count * (heads // kv_heads) >= 128
 
 
 class GQAAttention(Part):
@@ -112,6 +125,9 @@ class GQAAttention(Part):
             scratch = ws.take((floats,), torch.float32) if floats else None
             ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
                                  s.head_dim, view.window, self.scale, splits, scratch, b.stream)
+        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count):
+            ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
+                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
         else:
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
                                   s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)

@@ -142,6 +142,10 @@ def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed)
     elif kind == "prefill":
         o.attention_prefill(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)),
                             d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale)
+    elif kind == "tc":
+        o.attention_tc(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)),
+                       d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale)
+        o.gemm_tc_check(DEV)
     else:
         splits = kind
         floats = o.decode_scratch_floats(len(counts), heads, hd, splits)
@@ -167,6 +171,46 @@ def test_attention_prefill_tensor_cores(heads, kv_heads, hd):
     run_attention("prefill", bf, heads, kv_heads, hd, pasts=[70, 0, 129, 5], counts=[33, 5, 1, 130], window=0, seed=2)
     run_attention("prefill", bf, heads, kv_heads, hd, pasts=[0, 150], counts=[170, 40], window=50, seed=3)
     run_attention("prefill", bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 128), (4, 1, 64), (8, 8, 64), (16, 2, 128), (2, 2, 128), (32, 1, 64)])
+def test_attention_tcgen05(heads, kv_heads, hd):
+    """The tcgen05 kernel on the cases of the mma.sync kernel (pools are NaN outside the sequences), and on
+    longer prompts that cross many pages and tiles."""
+    bf = torch.bfloat16
+    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 0, 0], counts=[1, 64, 200], window=0, seed=1)
+    run_attention("tc", bf, heads, kv_heads, hd, pasts=[70, 0, 129, 5], counts=[33, 5, 1, 130], window=0, seed=2)
+    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 150], counts=[170, 40], window=50, seed=3)
+    run_attention("tc", bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
+    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 37], counts=[700, 450], window=0, seed=5)
+
+
+def test_attention_tcgen05_growing_scores():
+    """Scores that grow along the sequence force the running maximum up page after page, so the accumulator in
+    tensor memory is rescaled many times; scores that shrink never rescale it. Both must agree with the reference."""
+    o = ops()
+    bf = torch.bfloat16
+    H, K, hd, L = 4, 2, 128, 600
+    for direction in (1.0, -1.0):
+        gen = torch.Generator().manual_seed(11)
+        k_pool, v_pool, table, ks, vs = make_cache([L], K, hd, bf, gen)
+        q = torch.randn(L, H, hd, generator=gen).to(bf)
+        # key t gets an extra component along a fixed direction, growing (or shrinking) with t; every query has that component
+        ramp = (torch.arange(L, dtype=torch.float32) / L * 12.0 * direction)
+        for t in range(L):
+            page, row = int(table[0, t // 64]), t % 64
+            k_pool[page, :, row, 0] = ramp[t].to(bf)
+            ks[0][t, :, 0] = ramp[t].to(bf)
+        q[:, :, 0] = 8.0
+        d = lambda a: torch.as_tensor(a).to(DEV)
+        i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        out = torch.empty(L, H * hd, dtype=bf, device=DEV)
+        o.attention_tc(d(q), d(k_pool), d(v_pool), out, i32(0, L), i32(0), i32(L), d(table), L, H, K, hd, 0, 1.0)
+        o.gemm_tc_check(DEV)
+        ref = plain_attention(q.double(), ks[0].double(), vs[0].double(), list(range(L)), 0, 1.0)
+        got = out.cpu().double().view(L, H, hd)
+        assert torch.isfinite(got).all()
+        torch.testing.assert_close(got, ref, rtol=2e-2, atol=1.5e-2)
 
 
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
