@@ -46,6 +46,17 @@ struct AttnTcArgs {
   int* status;
 };
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+
 template <int HD>
 struct AttnTcLayout {
   static constexpr int Q_BYTES = kAtRows * HD * 2;
@@ -191,8 +202,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int pos = R < rows_total ? past + R / G : -1;        // -1: a padding row sees nothing
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    const int tile_pos_min = past + t_first;
-    const int tile_lo_max = a.window > 0 ? max(0, past + t_last - a.window + 1) : 0;
     float m_used = -INFINITY, l = 0.0f;
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
@@ -213,24 +222,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty + 8 * b);
 
-      const bool need_mask = key0 + 63 > tile_pos_min || key0 < tile_lo_max || R >= rows_total;
+      // raw scores -> masked raw scores and their maximum; the mask costs two compares and a select per score, so
+      // only warps with a row that needs it (the diagonal, a window's edge, padding) run it
       float mx = -INFINITY;
+      if (__any_sync(0xffffffffu, key0 + 63 > pos || key0 < lo)) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float v = __uint_as_float(sr[c >> 5][c & 31]) * a.scale_log2;
-        if (need_mask) {
+        for (int c = 0; c < 64; ++c) {
           const int key = key0 + c;
-          if (key > pos || key < lo) v = -INFINITY;
+          if (key > pos || key < lo) sr[c >> 5][c & 31] = 0xff800000u;     // -inf
         }
-        sr[c >> 5][c & 31] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
       }
-      const float m_new = fmaxf(m_used, mx);
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+      const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         if (!wait_all(pv_done, (j - 1) & 1, 29)) { ok = false; break; }
         tc_fence_after();
-        const float alpha = grow ? exp2f(m_used - m_new) : 1.0f;
+        const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t o[32];
@@ -243,16 +252,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_before();
       }
       if (grow) m_used = m_new;
-      const float m_safe = m_used == -INFINITY ? 0.0f : m_used;
+      const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
       uint32_t pk[32];
+      float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = exp2f(__uint_as_float(sr[c >> 5][c & 31]) - m_safe);
-        const float p1 = exp2f(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_safe);
-        l += p0 + p1;
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), a.scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), a.scale_log2, neg_m));
+        l0 += p0;
+        l1 += p1;
         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
       }
+      l += l0 + l1;
       if (j > 0 && !wait_all(pv_done, (j - 1) & 1, 30)) { ok = false; break; }     // the last product has read P
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
@@ -357,6 +369,7 @@ extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v
   SLB_REQUIRE(slb_attention_tc_supported(heads, kv_heads, head_dim),
               "attention (tcgen05): heads=%d kv_heads=%d head_dim=%d is not taken (head size 64 or 128, group size a divisor of 128)",
               heads, kv_heads, head_dim);
+  SLB_REQUIRE(scale > 0.0f, "attention (tcgen05): the kernel takes a positive scale, got %g", (double)scale);
   SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && window >= 0 && table_stride > 0 && n_seqs < 65536 && kv_heads < 65536 &&
               tokens >= 0 && pool_pages > 0 && status != nullptr,
               "attention (tcgen05): seqs=%d max_count=%d window=%d table_stride=%d", n_seqs, max_count, window, table_stride);

@@ -31,8 +31,8 @@ from .spec import AttentionSpec
 ATTENTION_CHOICE = os.environ.get("SLEUTH_B200_ATTENTION", "auto")
 
 
-def use_tc_attention(heads: int, kv_heads: int, head_dim: int, dtype, max_count: int) -> bool:
-    if ATTENTION_CHOICE == "mma" or not ops.attention_tc_supported(heads, kv_heads, head_dim, dtype):
+def use_tc_attention(heads: int, kv_heads: int, head_dim: int, dtype, max_count: int, scale: float = 1.0) -> bool:
+    if ATTENTION_CHOICE == "mma" or scale <= 0 or not ops.attention_tc_supported(heads, kv_heads, head_dim, dtype):
         return False
     return ATTENTION_CHOICE == "tc" or max_count * (heads // kv_heads) >= 128
 
@@ -125,7 +125,7 @@ class GQAAttention(Part):
             scratch = ws.take((floats,), torch.float32) if floats else None
             ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
                                  s.head_dim, view.window, self.scale, splits, scratch, b.stream)
-        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count):
+        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
             ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
                              s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
         else:
