@@ -7,20 +7,22 @@
 // serves all G heads of the group.
 //
 // A block takes 128 rows and walks over the pages (64 keys each) that those rows may see:
-//   * warp 0, one lane: TMA producer. The 128 x HD query tile once (a 3-D box over [tokens, heads, HD]), then for
-//     every page the key tile and the value tile [64, HD] straight from the pool, two stages each, all in the
-//     128-byte-swizzled layout that the tensor core reads.
-//   * warp 1, one lane: MMA issuer. S = Q K^T (M = 128, N = 64) into one of two score buffers in tensor memory, so
-//     that the scores of page j + 1 are computed while the softmax of page j runs; then O += P V (M = 128, N = HD),
-//     with P read from shared memory and V read in place as an N-major operand.
-//   * warps 2 to 5: softmax, one row per thread. They read a score row from tensor memory, scale and mask it, keep
-//     the running maximum and sum, write P as bfloat16 into shared memory, and when a row's maximum has grown by
-//     more than 2^8 since O was last scaled, rescale O in tensor memory (otherwise the old maximum keeps serving:
-//     exact in float32, since numerator and denominator carry the same factor). At the end they divide by the sum
-//     and store. Value rows of the last page that lie beyond the sequence are zeroed in shared memory before the
-//     product, so that leftovers of an earlier tenant of the page cannot reach the sum (0 * inf).
-// Two blocks fit on an SM (112 KB of shared memory and 256 columns of tensor memory each for HD = 128); while one
-// waits for its softmax the other's products keep the tensor core busy.
+//   * warp 0, one lane: the scores. It asks TMA for the 128 x HD query tile once (a 3-D box over [tokens, heads, HD])
+//     and for the key page [64, HD] of every step, two stages, straight from the pool in the 128-byte-swizzled layout
+//     that the tensor core reads, and issues S = Q K^T (M = 128, N = 64) into one of two score buffers in tensor
+//     memory, one page ahead of the softmax.
+//   * warp 1, one lane: the values. It asks TMA for the value pages and issues O += P V (M = 128, N = HD) as soon as
+//     the softmax has written P into shared memory; V is read in place as an N-major operand.
+//   * warps 2 to 9: softmax, two threads per row (keys 0..31 and 32..63 of the page). They read their half of a score
+//     row from tensor memory, mask it, agree on the row's maximum through shared memory, write P as bfloat16 into
+//     shared memory, and when a row's maximum has grown by more than 2^8 since O was last scaled, rescale O in
+//     tensor memory (otherwise the old maximum keeps serving: exact, since numerator and denominator carry the
+//     same factor). At the end they add their sums, divide and store. Value rows of the last page that lie beyond
+//     the sequence are zeroed in shared memory before the product, so that leftovers of an earlier tenant of the
+//     page cannot reach the sum (0 * inf).
+// Two blocks fit on an SM (113 KB of shared memory and 256 columns of tensor memory each); while one waits for its
+// softmax the other's products keep the tensor core busy. A block's own chain per page (scores -> softmax -> P ->
+// product) is what bounds a single long prompt; many sequences or heads fill the GPU.
 //
 // Every wait is bounded; a wait that gives up writes a code into `status`, and the block still frees its tensor
 // memory and returns. TMA loads never use cluster multicast.
@@ -30,7 +32,7 @@
 
 namespace slb {
 
-constexpr int kAtThreads = 192;
+constexpr int kAtThreads = 320;      // producer warp, MMA warp, eight softmax warps
 constexpr int kAtRows = 128;
 constexpr float kRescaleStep = 8.0f;     // in log2 units
 
@@ -67,8 +69,10 @@ struct AttnTcLayout {
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES; // two stages
   static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
   static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  static constexpr int N_BARS = 15;
-  static constexpr int TOTAL = BAR_OFF + N_BARS * 8 + 16;
+  static constexpr int N_BARS = 20;
+  static constexpr int XCH_OFF = BAR_OFF + N_BARS * 8 + 16;   // row maxima as 16-bit values, [2 halves][128 rows]
+  static constexpr int TOTAL = XCH_OFF + 2 * kAtRows * 2;
+  static_assert(2 * (TOTAL + 1024) <= 228 * 1024, "two blocks must fit on an SM");
   static constexpr int TMEM_COLS = 256;              // S0, S1 (64 each) and O (HD <= 128)
 };
 
@@ -86,8 +90,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   }
   const uint32_t sQ = base + L::Q_OFF, sK = base + L::K_OFF, sV = base + L::V_OFF, sP = base + L::P_OFF;
   const uint32_t bars = base + L::BAR_OFF;
-  const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56,
-                 s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_done = bars + 112;
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, s_full = bars + 40, s_empty = bars + 56,
+                 pv_done = bars + 72, p_full = bars + 88, xw_bar = bars + 96, xr_bar = bars + 128;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + L::N_BARS * 8);
 
   const int seq = blockIdx.z, kh = blockIdx.y;
@@ -110,14 +114,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(k_full + 8 * i, 1);
-      mbar_init(k_empty + 8 * i, 1);
       mbar_init(v_full + 8 * i, 1);
-      mbar_init(v_empty + 8 * i, 1);
       mbar_init(s_full + 8 * i, 1);
-      mbar_init(s_empty + 8 * i, 4);     // one arrival per softmax warp
+      mbar_init(pv_done + 8 * i, 1);
+      mbar_init(s_empty + 8 * i, 8);     // one arrival per softmax warp
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 4; ++i) {          // the two warps that share a quarter of the rows
+      mbar_init(xw_bar + 8 * i, 2);
+      mbar_init(xr_bar + 8 * i, 2);
+    }
+    mbar_init(p_full, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -136,35 +142,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---- producer ----
+      // ---- scores: loads Q and the key pages, issues S_j = Q K_j^T one page ahead of the softmax ----
+      constexpr uint32_t idesc_s = instr_desc(kAtRows, 64);
+      auto load_keys = [&](int j) {
+        const int s = j & 1;
+        const int row0 = (table[page_lo + j] * a.kv_heads + kh) * 64;
+        mbar_expect_tx(k_full + 8 * s, L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) tma_load_2d(sK + s * L::KV_BYTES + h * 8192, &map_k, h * 64, row0, k_full + 8 * s);
+      };
       mbar_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
       for (int h = 0; h < HD / 64; ++h)
         tma_load_3d(sQ + h * (kAtRows * 128), &map_q, h * 64, kh * G, tok0 + t_first, q_full);
-      for (int j = 0; j < n_pages; ++j) {
-        const int s = j & 1;
-        const int row0 = (table[page_lo + j] * a.kv_heads + kh) * 64;
-        if (j >= 2 && !mbar_wait(k_empty + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 21); break; }
-        mbar_expect_tx(k_full + 8 * s, L::KV_BYTES);
-#pragma unroll
-        for (int h = 0; h < HD / 64; ++h) tma_load_2d(sK + s * L::KV_BYTES + h * 8192, &map_k, h * 64, row0, k_full + 8 * s);
-        if (j >= 2 && !mbar_wait(v_empty + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 22); break; }
-        mbar_expect_tx(v_full + 8 * s, L::KV_BYTES);
-#pragma unroll
-        for (int h = 0; h < HD / 64; ++h) tma_load_2d(sV + s * L::KV_BYTES + h * 8192, &map_v, h * 64, row0, v_full + 8 * s);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer ----
-      constexpr uint32_t idesc_s = instr_desc(kAtRows, 64);
-      constexpr uint32_t idesc_o = instr_desc(kAtRows, HD, true);
+      load_keys(0);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(a.status, 23);
-      auto issue_scores = [&](int j) -> bool {
+      for (int j = 0; j < n_pages && ok; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 24); return false; }
-        if (j >= 2 && !mbar_wait(s_empty + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 25); return false; }
+        if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 24); break; }
+        if (j >= 2 && !mbar_wait(s_empty + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 25); break; }   // the softmax has read S_{j-2}
         tc_fence_after();
 #pragma unroll
         for (int h = 0; h < HD / 64; ++h) {
@@ -173,16 +170,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int k4 = 0; k4 < 4; ++k4)
             mma_bf16_ss(tmem + (uint32_t)(s * 64), dq + (uint64_t)(k4 * 2), dk + (uint64_t)(k4 * 2), idesc_s, (h > 0 || k4 > 0) ? 1u : 0u);
         }
-        mma_commit(s_full + 8 * s);
-        mma_commit(k_empty + 8 * s);
-        return true;
-      };
-      if (ok) ok = issue_scores(0);
-      for (int j = 0; j < n_pages && ok; ++j) {
+        mma_commit(s_full + 8 * s);          // S_j is complete: the softmax may read it, and this key stage is free again
+        if (j + 1 < n_pages) {
+          // the other key stage was read by S_{j-1}, issued a whole page ago
+          if (j >= 1 && !mbar_wait(s_full + 8 * (s ^ 1), ((j - 1) >> 1) & 1)) { atomicExch(a.status, 21); break; }
+          load_keys(j + 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- values: loads the value pages, issues O += P_j V_j as soon as the softmax has written P_j ----
+      constexpr uint32_t idesc_o = instr_desc(kAtRows, HD, true);
+      auto load_values = [&](int j) {
         const int s = j & 1;
-        if (j + 1 < n_pages && !issue_scores(j + 1)) break;
-        if (!mbar_wait(p_full, j & 1)) { atomicExch(a.status, 26); break; }
+        const int row0 = (table[page_lo + j] * a.kv_heads + kh) * 64;
+        mbar_expect_tx(v_full + 8 * s, L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) tma_load_2d(sV + s * L::KV_BYTES + h * 8192, &map_v, h * 64, row0, v_full + 8 * s);
+      };
+      load_values(0);
+      for (int j = 0; j < n_pages; ++j) {
+        const int s = j & 1;
         if (!mbar_wait(v_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 27); break; }
+        if (!mbar_wait(p_full, j & 1)) { atomicExch(a.status, 26); break; }
         tc_fence_after();
         const uint64_t dp = smem_desc(sP);
 #pragma unroll
@@ -190,124 +201,147 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const uint64_t dv = smem_desc_mn(sV + s * L::KV_BYTES + k4 * 2048, 8192, 1024);
           mma_bf16_ss(tO, dp + (uint64_t)(k4 * 2), dv, idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
         }
-        mma_commit(pv_done);
-        mma_commit(v_empty + 8 * s);
+        mma_commit(pv_done + 8 * s);         // P and this value stage are free again when it fires
+        if (j + 1 < n_pages) {
+          if (j >= 1 && !mbar_wait(pv_done + 8 * (s ^ 1), ((j - 1) >> 1) & 1)) { atomicExch(a.status, 22); break; }
+          load_values(j + 1);
+        }
       }
     }
   } else {
-    // ---- softmax: warps 2..5, tensor-memory lanes 32 * (warp % 4) .. + 31; thread = row ----
-    const int quad = warp & 3;
+    // ---- softmax: warps 2..9. Tensor-memory lanes 32 * (warp % 4) .. + 31 hold the rows; two warps share those
+    // lanes, one for keys 0..31 of the page, one for keys 32..63: two threads per row ----
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int R = r0 + r;
     const int pos = R < rows_total ? past + R / G : -1;        // -1: a padding row sees nothing
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    const uint32_t xw = xw_bar + 8 * quad, xr = xr_bar + 8 * quad;
+    unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 halves][128 rows]
     float m_used = -INFINITY, l = 0.0f;
     bool ok = true;
-    auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
-      bool ready = true;
-      if (lane == 0) ready = mbar_wait(bar, parity);
-      ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+    auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+      const bool ready = mbar_wait(bar, parity);       // every lane polls: no divergence, no shuffle
       if (!ready && lane == 0) atomicExch(a.status, code);
       return ready;
     };
-    for (int j = 0; j < n_pages; ++j) {
-      const int b = j & 1, key0 = (page_lo + j) * 64;
-      if (!wait_all(s_full + 8 * b, (j >> 1) & 1, 28)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sr[2][32];
-      tmem_ld32(lane_addr + (uint32_t)(b * 64), sr[0]);
-      tmem_ld32(lane_addr + (uint32_t)(b * 64 + 32), sr[1]);
-      tc_fence_before();
+    auto arrive_warp = [&](uint32_t bar) {
       __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty + 8 * b);
+      if (lane == 0) mbar_arrive(bar);
+    };
+    for (int j = 0; j < n_pages; ++j) {
+      const int b = j & 1, key0 = (page_lo + j) * 64 + half * 32;
+      if (!wait_warp(s_full + 8 * b, (j >> 1) & 1, 28)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[32];
+      tmem_ld32(lane_addr + (uint32_t)(b * 64 + half * 32), sr);
+      tc_fence_before();
+      arrive_warp(s_empty + 8 * b);
 
       // raw scores -> masked raw scores and their maximum; the mask costs two compares and a select per score, so
       // only warps with a row that needs it (the diagonal, a window's edge, padding) run it
-      float mx = -INFINITY;
-      if (__any_sync(0xffffffffu, key0 + 63 > pos || key0 < lo)) {
+      if (__any_sync(0xffffffffu, key0 + 31 > pos || key0 < lo)) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int key = key0 + c;
-          if (key > pos || key < lo) sr[c >> 5][c & 31] = 0xff800000u;     // -inf
+          if (key > pos || key < lo) sr[c] = 0xff800000u;     // -inf
         }
       }
+      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+      for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+      // The row's maximum is the larger of the two halves'. They are exchanged rounded up to 16 bits (any common
+      // reference at or above the maximum serves a softmax), so both threads of a row take the same decisions.
+      {
+        const uint32_t bits = __float_as_uint(mx);
+        const unsigned short up = (unsigned short)(((bits & 0x80000000u) ? bits : bits + 0xffffu) >> 16);
+        if (j > 0 && !wait_warp(xr, (j - 1) & 1, 33)) { ok = false; break; }      // the partner has read the last one
+        xch[half * 128 + r] = up;
+        arrive_warp(xw);
+        if (!wait_warp(xw, j & 1, 34)) { ok = false; break; }
+        const unsigned short other = xch[(half ^ 1) * 128 + r];
+        arrive_warp(xr);
+        mx = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
+      }
       const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        if (!wait_all(pv_done, (j - 1) & 1, 29)) { ok = false; break; }
+        if (!wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29)) { ok = false; break; }
         tc_fence_after();
         const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld32(lane_addr + 128 + c0, o);
+        for (int c0 = 0; c0 < HD / 2; c0 += 16) {      // this thread's half of the accumulator row
+          uint32_t o[16];
+          tmem_ld16(lane_addr + 128 + half * (HD / 2) + c0, o);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-          tmem_st32(lane_addr + 128 + c0, o);
+          for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          tmem_st16(lane_addr + 128 + half * (HD / 2) + c0, o);
         }
         l *= alpha;
         tc_fence_before();
       }
       if (grow) m_used = m_new;
       const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
-      uint32_t pk[32];
+      uint32_t pk[16];
       float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), a.scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), a.scale_log2, neg_m));
+      for (int c = 0; c < 32; c += 2) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
         l0 += p0;
         l1 += p1;
         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
       }
       l += l0 + l1;
-      if (j > 0 && !wait_all(pv_done, (j - 1) & 1, 30)) { ok = false; break; }     // the last product has read P
+      if (j > 0 && !wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 30)) { ok = false; break; }     // the last product has read P
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t dst = sP + (uint32_t)(r * 128 + ((ch ^ (r & 7)) << 4));
+      for (int ch = 0; ch < 4; ++ch) {
+        const uint32_t dst = sP + (uint32_t)(r * 128 + (((half * 4 + ch) ^ (r & 7)) << 4));
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * ch]), "r"(pk[4 * ch + 1]),
                      "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3]) : "memory");
       }
-      const int valid = seq_len - key0;          // rows of this page that belong to the sequence
+      const int valid = seq_len - (page_lo + j) * 64;          // rows of this page that belong to the sequence
       if (valid < 64) {
-        if (!wait_all(v_full + 8 * b, (j >> 1) & 1, 31)) { ok = false; break; }
-        if (r < 64 && r >= valid) {
+        if (!wait_warp(v_full + 8 * b, (j >> 1) & 1, 31)) { ok = false; break; }
+        if (r < 64 && r >= valid && half < HD / 64) {          // each half clears one 64-wide slab of the row
 #pragma unroll
-          for (int h = 0; h < HD / 64; ++h)
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-              const uint32_t dst = sV + (uint32_t)(b * L::KV_BYTES + h * 8192 + r * 128 + ch * 16);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
-            }
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t dst = sV + (uint32_t)(b * L::KV_BYTES + half * 8192 + r * 128 + ch * 16);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+          }
         }
       }
       fence_smem_to_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      arrive_warp(p_full);
     }
-    if (ok && wait_all(pv_done, (n_pages - 1) & 1, 32)) {
+    if (ok && wait_warp(pv_done + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, 32)) {
       tc_fence_after();
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      __nv_bfloat16* dst = a.out + ((size_t)(tok0 + (R < rows_total ? R / G : 0)) * a.heads + kh * G + R % G) * HD;
+      // the row's sum is the two halves' sums; they meet in the P tile, which the last product has finished reading
+      float* xl = reinterpret_cast<float*>(smem + L::P_OFF);
+      xl[half * 128 + r] = l;
+      arrive_warp(xw);
+      if (wait_warp(xw, n_pages & 1, 35)) {
+        l += xl[(half ^ 1) * 128 + r];
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        __nv_bfloat16* dst = a.out + ((size_t)(tok0 + (R < rows_total ? R / G : 0)) * a.heads + kh * G + R % G) * HD + half * (HD / 2);
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t o[32];
-        tmem_ld32(lane_addr + 128 + c0, o);
-        if (R < rows_total) {
+        for (int c0 = 0; c0 < HD / 2; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(lane_addr + 128 + half * (HD / 2) + c0, o);
+          if (R < rows_total) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 q;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-            q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
-            q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + c0 + c) = q;
+            for (int c = 0; c < 16; c += 8) {
+              uint4 q;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+              q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
+              q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + c0 + c) = q;
+            }
           }
         }
       }
