@@ -28,7 +28,7 @@ constexpr int kTcBK = 64;             // bf16 elements per slice: 128 bytes, one
 constexpr int kTcStages = 4;
 constexpr int kTcThreads = 192;       // producer warp, MMA warp, four epilogue warps
 
-enum TcMode : int { kTcBf16 = 0, kTcF32 = 1, kTcAddF32 = 2, kTcSwiglu = 3 };
+enum TcMode : int { kTcBf16 = 0, kTcF32 = 1, kTcAddF32 = 2, kTcSwiglu = 3, kTcQkv = 4 };
 
 struct TcArgs {
   void* C;
@@ -36,6 +36,98 @@ struct TcArgs {
   int up_row0;          // kTcSwiglu: first up row in W (= number of gate rows)
   int* status;          // 0 = fine; else a code saying which wait gave up
 };
+
+// kTcQkv: what follows the fused q/k/v projection, done on the accumulator rows (float32) before anything is
+// rounded: bias, per-head RMSNorm of q and k, rotation of the whole head, and the store of q into [tokens, H, hd]
+// and of k and v into the token's cache page (sleuth/forge/model/attention.py:121-130, rotation
+// sleuth/forge/model/rope.py:41-55). A tile covers whole heads: BN is a multiple of head_dim.
+struct TcQkv {
+  const float* bias;        // [(H + 2K) * hd] or null
+  const float* q_gain;      // [hd] or null (no QK-norm)
+  const float* k_gain;
+  const float* cos_table;   // [positions, hd / 2] or null (no rotation)
+  const float* sin_table;
+  __nv_bfloat16* q_out;     // [tokens, H, hd]
+  __nv_bfloat16* k_pool;    // [pages, K, 64, hd]; null when the projection holds only q heads
+  __nv_bfloat16* v_pool;
+  const int* tok_seq;       // [tokens]
+  const int* tok_pos;       // [tokens]
+  const int* block_table;   // [seqs, table_stride]
+  int table_stride, heads, kv_heads, head_dim;
+  float eps;
+};
+
+// One head of one row: `taddr` is this thread's lane at the head's first accumulator column.
+template <int HD>
+__device__ __forceinline__ void qkv_head_epilogue(const TcQkv& q, uint32_t taddr, int row, int M, int head) {
+  float v[HD];
+#pragma unroll
+  for (int c0 = 0; c0 < HD; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c0, r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(r[j]);
+  }
+  if (row >= M || head >= q.heads + 2 * q.kv_heads) return;
+  if (q.bias) {
+    const float4* b = reinterpret_cast<const float4*>(q.bias + (size_t)head * HD);
+#pragma unroll
+    for (int c = 0; c < HD; c += 4) {
+      const float4 t = b[c >> 2];
+      v[c] += t.x; v[c + 1] += t.y; v[c + 2] += t.z; v[c + 3] += t.w;
+    }
+  }
+  const bool is_q = head < q.heads, is_k = !is_q && head < q.heads + q.kv_heads;
+  const int pos = q.tok_pos[row];
+  if (is_q || is_k) {
+    const float* gain = is_q ? q.q_gain : q.k_gain;
+    if (gain) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int c = 0; c < HD; ++c) ss = fmaf(v[c], v[c], ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + q.eps);
+      const float4* g = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+      for (int c = 0; c < HD; c += 4) {
+        const float4 t = g[c >> 2];
+        v[c] = (v[c] * inv) * t.x; v[c + 1] = (v[c + 1] * inv) * t.y;
+        v[c + 2] = (v[c + 2] * inv) * t.z; v[c + 3] = (v[c + 3] * inv) * t.w;
+      }
+    }
+    if (q.cos_table) {
+      const float4* cs = reinterpret_cast<const float4*>(q.cos_table + (size_t)pos * (HD / 2));
+      const float4* sn = reinterpret_cast<const float4*>(q.sin_table + (size_t)pos * (HD / 2));
+#pragma unroll
+      for (int c = 0; c < HD / 2; c += 4) {
+        const float4 co = cs[c >> 2], si = sn[c >> 2];
+        const float cc[4] = {co.x, co.y, co.z, co.w}, ssn[4] = {si.x, si.y, si.z, si.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x = v[c + e], y = v[c + e + HD / 2];
+          v[c + e] = x * cc[e] + (-y) * ssn[e];
+          v[c + e + HD / 2] = y * cc[e] + x * ssn[e];
+        }
+      }
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q.q_out + ((size_t)row * q.heads + head) * HD;
+  } else {
+    const int kh = is_k ? head - q.heads : head - q.heads - q.kv_heads;
+    const int page = q.block_table[(size_t)q.tok_seq[row] * q.table_stride + pos / 64];
+    dst = (is_k ? q.k_pool : q.v_pool) + (((size_t)page * q.kv_heads + kh) * 64 + (pos % 64)) * HD;
+  }
+#pragma unroll
+  for (int c = 0; c < HD; c += 8) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[c], v[c + 1]), p1 = __floats2bfloat162_rn(v[c + 2], v[c + 3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[c + 4], v[c + 5]), p3 = __floats2bfloat162_rn(v[c + 6], v[c + 7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(dst + c) = o;
+  }
+}
 
 __device__ __forceinline__ float fast_silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
@@ -81,9 +173,9 @@ __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, 
 
 // Persistent: a block walks the output tiles blockIdx.x, blockIdx.x + gridDim.x, ... Two accumulators in tensor
 // memory alternate, so the epilogue warps drain tile t while the tensor core already works on tile t + 1.
-template <int BN>
+template <int BN, bool QKV>
 __global__ void __launch_bounds__(kTcThreads)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a, TcQkv qa) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,6 +289,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + quad * 32 + lane;
       const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+      if constexpr (QKV) {
+        if (qa.head_dim == 128) {
+          for (int c = 0; c < BN; c += 128) qkv_head_epilogue<128>(qa, lane_base + c, row, a.M, (n0 + c) / 128);
+        } else {
+          for (int c = 0; c < BN; c += 64) qkv_head_epilogue<64>(qa, lane_base + c, row, a.M, (n0 + c) / 64);
+        }
+      } else
       for (int c = 0; c < cols_per_tile; c += 32) {
         uint32_t r[32];
         float v[32];
@@ -240,12 +339,12 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-template <int BN>
-static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s) {
+template <int BN, bool QKV = false>
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s, const TcQkv& qa = TcQkv{}) {
   const int smem = kTcStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kTcStages + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(2, "gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
@@ -258,7 +357,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs&
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
   dim3 grid((unsigned)(total < sms ? total : sms));
-  launch_prefetching(gemm_tc_kernel<BN>, grid, dim3(kTcThreads), (size_t)smem, s, mx, mw, a);
+  launch_prefetching(gemm_tc_kernel<BN, QKV>, grid, dim3(kTcThreads), (size_t)smem, s, mx, mw, a, qa);
   return check_launch("gemm_tc");
 }
 
@@ -297,4 +396,44 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
     case 64: return launch_tc<64>(mx, mw, a, s);
     default: return launch_tc<32>(mx, mw, a, s);
   }
+}
+
+// The fused q/k/v projection of a step with many tokens: X [M, K] times W [(H + 2 * kv_heads) * head_dim, K]^T, and on
+// the float32 accumulators bias, per-head RMSNorm of q and k (gains given), rotation of the whole head (tables
+// [positions, head_dim / 2] given) and the stores: q into q_out [M, H, head_dim], k and v into the cache page of each
+// token (block_table[tok_seq, tok_pos / 64], row tok_pos % 64). kv_heads == 0: the projection holds only q heads.
+extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int heads, int kv_heads, int head_dim,
+                               const float* bias, const float* q_gain, const float* k_gain, const float* cos_table,
+                               const float* sin_table, float eps, void* q_out, void* k_pool, void* v_pool,
+                               const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride,
+                               int* status, void* stream) {
+  SLB_REQUIRE(head_dim == 64 || head_dim == 128, "gemm_tc_qkv: head size 64 or 128, got %d", head_dim);
+  SLB_REQUIRE(heads > 0 && kv_heads >= 0, "gemm_tc_qkv: heads=%d kv_heads=%d", heads, kv_heads);
+  const int N = (heads + 2 * kv_heads) * head_dim;
+  SLB_REQUIRE(slb_gemm_tc_supported(M, N, K), "gemm_tc_qkv: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
+  SLB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr) || kv_heads == 0, "gemm_tc_qkv: q and k gains go together");
+  SLB_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "gemm_tc_qkv: cos and sin tables go together");
+  SLB_REQUIRE(q_out != nullptr && tok_pos != nullptr && status != nullptr, "gemm_tc_qkv: q_out, tok_pos and status are needed");
+  SLB_REQUIRE(kv_heads == 0 || (k_pool && v_pool && tok_seq && block_table && table_stride > 0),
+              "gemm_tc_qkv: the cache pools and the block table are needed to store keys and values");
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+              ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
+              ((uintptr_t)q_gain % 16 == 0) && ((uintptr_t)k_gain % 16 == 0) && ((uintptr_t)cos_table % 16 == 0) &&
+              ((uintptr_t)sin_table % 16 == 0), "gemm_tc_qkv: every tensor must be 16-byte aligned");
+  const long long m_tiles = (M + 127) / 128;
+  const int bn = m_tiles * ((N + 255) / 256) >= 100 ? 256 : 128;
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, X, M, K, kTcBM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, 128);
+  if (rc) return rc;
+  TcArgs a;
+  a.C = nullptr; a.M = M; a.N = N; a.K = K; a.ldc = N; a.mode = kTcQkv; a.up_row0 = N; a.status = status;
+  TcQkv qa;
+  qa.bias = bias; qa.q_gain = q_gain; qa.k_gain = k_gain; qa.cos_table = cos_table; qa.sin_table = sin_table;
+  qa.q_out = (__nv_bfloat16*)q_out; qa.k_pool = (__nv_bfloat16*)k_pool; qa.v_pool = (__nv_bfloat16*)v_pool;
+  qa.tok_seq = tok_seq; qa.tok_pos = tok_pos; qa.block_table = block_table; qa.table_stride = table_stride;
+  qa.heads = heads; qa.kv_heads = kv_heads; qa.head_dim = head_dim; qa.eps = eps;
+  cudaStream_t s = (cudaStream_t)stream;
+  return bn == 256 ? launch_tc<256, true>(mx, mw, a, s, qa) : launch_tc<128, true>(mx, mw, a, s, qa);
 }

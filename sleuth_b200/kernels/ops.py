@@ -306,6 +306,29 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stre
                stream if stream is not None else current_stream())
 
 
+def gemm_tc_qkv(x, w, heads: int, kv_heads: int, head_dim: int, bias, q_gain, k_gain, cos, sin, eps: float, q_out,
+                k_pool, v_pool, tok_seq, tok_pos, block_table, stream=None) -> None:
+    """The fused q/k/v projection of many tokens with everything ``qkv_post`` does in its epilogue, on the float32
+    accumulators: bias, per-head RMSNorm of q and k, rotation of the whole head, q into ``q_out [T, H, hd]``, k and v
+    into each token's cache page. ``kv_heads == 0``: ``w`` holds only q heads and nothing is written to the cache."""
+    _cuda(x, w, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
+    M, K = x.shape
+    _need(x.dtype == w.dtype == q_out.dtype == torch.bfloat16, "gemm_tc_qkv: bfloat16 only")
+    _need(w.shape == ((heads + 2 * kv_heads) * head_dim, K) and w.is_contiguous() and x.is_contiguous(), "gemm_tc_qkv: weight shape")
+    _need(q_out.shape == (M, heads, head_dim) and q_out.is_contiguous(), "gemm_tc_qkv: q_out shape")
+    for v in (bias, q_gain, k_gain, cos, sin):
+        _need(v is None or (v.dtype == torch.float32 and v.is_contiguous()), "gemm_tc_qkv: gains, biases and tables are float32")
+    _need(cos is None or (cos.shape[1] == head_dim // 2 and sin.shape == cos.shape), "gemm_tc_qkv: rotation tables [positions, hd / 2]")
+    _need(tok_pos.numel() >= M and (kv_heads == 0 or tok_seq.numel() >= M), "gemm_tc_qkv: per-token tables")
+    if kv_heads:
+        _need(k_pool is not None and tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape
+              and k_pool.dtype == v_pool.dtype == torch.bfloat16, "gemm_tc_qkv: pool shape")
+    lib().call("slb_gemm_tc_qkv", _p(x), _p(w), M, K, heads, kv_heads, head_dim, _p(bias), _p(q_gain), _p(k_gain), _p(cos),
+               _p(sin), float(eps), _p(q_out), _p(k_pool) if kv_heads else None, _p(v_pool) if kv_heads else None,
+               _p(tok_seq), _p(tok_pos), _p(block_table), 0 if block_table is None else block_table.shape[1],
+               _p(_tc_status(x.device)), stream if stream is not None else current_stream())
+
+
 def gemm_tc_check(device) -> None:
     """Raise if a tcgen05 product kernel gave up one of its bounded waits since the last check (synchronises)."""
     st = _TC_STATUS.get(str(torch.device(device)))

@@ -21,7 +21,8 @@ import torch
 from ..cache.paged import KVRequest
 from ..kernels import ops
 from .base import BuildContext, ParamDecl, Part, build_position, register_mixer
-from .linear import Linear
+from .base import Normed
+from .linear import Linear, use_tc
 from .spec import AttentionSpec
 
 
@@ -87,6 +88,26 @@ class GQAAttention(Part):
         return KVRequest(s.kv_heads, s.head_dim, s.window)
 
     # ---- one step ----
+    def _attend(self, q, y, b, view, table, ws):
+        """Attention of the step's (post-processed) queries over the cache into ``y``; the kernel by dtype and step shape."""
+        s = self.spec
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
+        if not flash:
+            ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
+                          s.head_dim, view.window, self.scale, b.stream)
+        elif b.max_count == 1:
+            splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
+            floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
+            scratch = ws.take((floats,), torch.float32) if floats else None
+            ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
+                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream)
+        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
+            ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
+                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
+        else:
+            ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
+                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
+
     def forward(self, h, x, b, view, ws):
         s = self.spec
         T = h.shape[0]
@@ -94,12 +115,27 @@ class GQAAttention(Part):
         kvh = 0 if s.reads_shared_kv else s.kv_heads
         table = b.tables[view.group]
         mark = ws.mark()
-        qkv = self.qkv.forward(h, ws=ws, stream=b.stream)
         tables = self.position.tables()
         cos, sin = tables if tables is not None else (None, None)
         rot = self.position.rot_dim
-        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
         flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
+        fused_post = (flash and rot in (0, s.head_dim) and b.max_count > 1 and (writes or s.reads_shared_kv)
+                      and use_tc(T, self.qkv.out_features, self.qkv.in_features))
+        if fused_post:
+            # many tokens: the projection's epilogue post-processes q/k/v on its float32 accumulators
+            q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
+            hh = h.tensor() if isinstance(h, Normed) else h
+            ops.gemm_tc_qkv(hh, self.qkv.weight, s.heads, kvh, s.head_dim, self.bias, self.q_gain, self.k_gain,
+                            cos if rot else None, sin if rot else None, s.qk_norm_eps, q,
+                            view.k_pool if kvh else None, view.v_pool if kvh else None, b.tok_seq, b.tok_pos, table,
+                            b.stream)
+            y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
+            self._attend(q, y, b, view, table, ws)
+            self.o.forward(y, into=x, ws=ws, stream=b.stream)
+            ws.release(mark)
+            return
+        qkv = self.qkv.forward(h, ws=ws, stream=b.stream)
+        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
         if flash and b.max_count == 1 and rot in (0, s.head_dim) and (writes or s.reads_shared_kv):
             # one token per sequence: the attention kernel post-processes q/k/v itself and appends to the cache
             splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
@@ -116,21 +152,7 @@ class GQAAttention(Part):
         ops.qkv_post(qkv, self.bias, self.q_gain, self.k_gain, cos, sin, q,
                      view.k_pool if writes else None, view.v_pool if writes else None,
                      b.tok_seq, b.tok_pos, table, s.heads, kvh, s.head_dim, rot, s.qk_norm_eps, b.stream)
-        if not flash:
-            ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
-                          s.head_dim, view.window, self.scale, b.stream)
-        elif b.max_count == 1:
-            splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
-            floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
-            scratch = ws.take((floats,), torch.float32) if floats else None
-            ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
-                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream)
-        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
-            ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
-        else:
-            ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
+        self._attend(q, y, b, view, table, ws)
         self.o.forward(y, into=x, ws=ws, stream=b.stream)
         ws.release(mark)
 
