@@ -57,75 +57,105 @@ struct TcQkv {
   float eps;
 };
 
-// One head of one row: `taddr` is this thread's lane at the head's first accumulator column.
+// One head of one row: `taddr` is this thread's lane at the head's first accumulator column. Two passes over the
+// accumulator keep the registers few: the first sums the squares, the second takes the channels in the pairs that
+// rotate together (c, c + HD / 2), 32 pairs at a time.
 template <int HD>
 __device__ __forceinline__ void qkv_head_epilogue(const TcQkv& q, uint32_t taddr, int row, int M, int head) {
-  float v[HD];
-#pragma unroll
-  for (int c0 = 0; c0 < HD; c0 += 32) {
-    uint32_t r[32];
-    tmem_ld32(taddr + c0, r);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(r[j]);
-  }
-  if (row >= M || head >= q.heads + 2 * q.kv_heads) return;
-  if (q.bias) {
-    const float4* b = reinterpret_cast<const float4*>(q.bias + (size_t)head * HD);
-#pragma unroll
-    for (int c = 0; c < HD; c += 4) {
-      const float4 t = b[c >> 2];
-      v[c] += t.x; v[c + 1] += t.y; v[c + 2] += t.z; v[c + 3] += t.w;
-    }
-  }
+  const bool live = row < M && head < q.heads + 2 * q.kv_heads;
   const bool is_q = head < q.heads, is_k = !is_q && head < q.heads + q.kv_heads;
-  const int pos = q.tok_pos[row];
-  if (is_q || is_k) {
-    const float* gain = is_q ? q.q_gain : q.k_gain;
-    if (gain) {
-      float ss = 0.0f;
+  const float* gain = (is_q || is_k) ? (is_q ? q.q_gain : q.k_gain) : nullptr;
+  const float* bias = q.bias ? q.bias + (size_t)head * HD : nullptr;
+  float inv = 1.0f;
+  if (gain) {          // uniform over the warp: every lane is in the same head
+    float ss = 0.0f;
 #pragma unroll
-      for (int c = 0; c < HD; ++c) ss = fmaf(v[c], v[c], ss);
-      const float inv = 1.0f / sqrtf(ss / (float)HD + q.eps);
-      const float4* g = reinterpret_cast<const float4*>(gain);
+    for (int c0 = 0; c0 < HD; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(taddr + c0, r);
+      if (live) {
 #pragma unroll
-      for (int c = 0; c < HD; c += 4) {
-        const float4 t = g[c >> 2];
-        v[c] = (v[c] * inv) * t.x; v[c + 1] = (v[c + 1] * inv) * t.y;
-        v[c + 2] = (v[c + 2] * inv) * t.z; v[c + 3] = (v[c + 3] * inv) * t.w;
-      }
-    }
-    if (q.cos_table) {
-      const float4* cs = reinterpret_cast<const float4*>(q.cos_table + (size_t)pos * (HD / 2));
-      const float4* sn = reinterpret_cast<const float4*>(q.sin_table + (size_t)pos * (HD / 2));
-#pragma unroll
-      for (int c = 0; c < HD / 2; c += 4) {
-        const float4 co = cs[c >> 2], si = sn[c >> 2];
-        const float cc[4] = {co.x, co.y, co.z, co.w}, ssn[4] = {si.x, si.y, si.z, si.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float x = v[c + e], y = v[c + e + HD / 2];
-          v[c + e] = x * cc[e] + (-y) * ssn[e];
-          v[c + e + HD / 2] = y * cc[e] + x * ssn[e];
+        for (int j = 0; j < 32; j += 4) {
+          float4 t = bias ? *reinterpret_cast<const float4*>(bias + c0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float x0 = __uint_as_float(r[j]) + t.x, x1 = __uint_as_float(r[j + 1]) + t.y;
+          const float x2 = __uint_as_float(r[j + 2]) + t.z, x3 = __uint_as_float(r[j + 3]) + t.w;
+          ss = fmaf(x0, x0, ss); ss = fmaf(x1, x1, ss); ss = fmaf(x2, x2, ss); ss = fmaf(x3, x3, ss);
         }
       }
     }
+    inv = 1.0f / sqrtf(ss / (float)HD + q.eps);
   }
-  __nv_bfloat16* dst;
-  if (is_q) {
-    dst = q.q_out + ((size_t)row * q.heads + head) * HD;
-  } else {
-    const int kh = is_k ? head - q.heads : head - q.heads - q.kv_heads;
-    const int page = q.block_table[(size_t)q.tok_seq[row] * q.table_stride + pos / 64];
-    dst = (is_k ? q.k_pool : q.v_pool) + (((size_t)page * q.kv_heads + kh) * 64 + (pos % 64)) * HD;
+  const int pos = live ? q.tok_pos[row] : 0;
+  __nv_bfloat16* dst = nullptr;
+  if (live) {
+    if (is_q) {
+      dst = q.q_out + ((size_t)row * q.heads + head) * HD;
+    } else {
+      const int kh = is_k ? head - q.heads : head - q.heads - q.kv_heads;
+      const int page = q.block_table[(size_t)q.tok_seq[row] * q.table_stride + pos / 64];
+      dst = (is_k ? q.k_pool : q.v_pool) + (((size_t)page * q.kv_heads + kh) * 64 + (pos % 64)) * HD;
+    }
   }
+  const bool rotate = q.cos_table != nullptr && (is_q || is_k);
+  constexpr int HALF = HD / 2;
 #pragma unroll
-  for (int c = 0; c < HD; c += 8) {
-    uint4 o;
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[c], v[c + 1]), p1 = __floats2bfloat162_rn(v[c + 2], v[c + 3]);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[c + 4], v[c + 5]), p3 = __floats2bfloat162_rn(v[c + 6], v[c + 7]);
-    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-    *reinterpret_cast<uint4*>(dst + c) = o;
+  for (int c0 = 0; c0 < HALF; c0 += 32) {
+    uint32_t ra[32], rb[32];
+    __syncwarp();                 // rows beyond the matrix skipped the arithmetic; the loads need the whole warp
+    tmem_ld32(taddr + c0, ra);
+    tmem_ld32(taddr + HALF + c0, rb);
+    if (!live) continue;
+    float x[32], y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      x[j] = __uint_as_float(ra[j]);
+      y[j] = __uint_as_float(rb[j]);
+    }
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(bias + c0 + j), u = *reinterpret_cast<const float4*>(bias + HALF + c0 + j);
+        x[j] += t.x; x[j + 1] += t.y; x[j + 2] += t.z; x[j + 3] += t.w;
+        y[j] += u.x; y[j + 1] += u.y; y[j + 2] += u.z; y[j + 3] += u.w;
+      }
+    }
+    if (gain) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(gain + c0 + j), u = *reinterpret_cast<const float4*>(gain + HALF + c0 + j);
+        x[j] = (x[j] * inv) * t.x; x[j + 1] = (x[j + 1] * inv) * t.y; x[j + 2] = (x[j + 2] * inv) * t.z; x[j + 3] = (x[j + 3] * inv) * t.w;
+        y[j] = (y[j] * inv) * u.x; y[j + 1] = (y[j + 1] * inv) * u.y; y[j + 2] = (y[j + 2] * inv) * u.z; y[j + 3] = (y[j + 3] * inv) * u.w;
+      }
+    }
+    if (rotate) {
+      const float* cs = q.cos_table + (size_t)pos * HALF + c0;
+      const float* sn = q.sin_table + (size_t)pos * HALF + c0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 co = *reinterpret_cast<const float4*>(cs + j), si = *reinterpret_cast<const float4*>(sn + j);
+        const float cc[4] = {co.x, co.y, co.z, co.w}, sv[4] = {si.x, si.y, si.z, si.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a0 = x[j + e], b0 = y[j + e];
+          x[j + e] = a0 * cc[e] + (-b0) * sv[e];
+          y[j + e] = b0 * cc[e] + a0 * sv[e];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 o;
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(x[j], x[j + 1]), p1 = __floats2bfloat162_rn(x[j + 2], x[j + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(x[j + 4], x[j + 5]), p3 = __floats2bfloat162_rn(x[j + 6], x[j + 7]);
+      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(dst + c0 + j) = o;
+      p0 = __floats2bfloat162_rn(y[j], y[j + 1]); p1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
+      p2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]); p3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
+      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(dst + HALF + c0 + j) = o;
+    }
   }
 }
 
@@ -173,8 +203,10 @@ __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, 
 
 // Persistent: a block walks the output tiles blockIdx.x, blockIdx.x + gridDim.x, ... Two accumulators in tensor
 // memory alternate, so the epilogue warps drain tile t while the tensor core already works on tile t + 1.
+// The q/k/v form has eight epilogue warps, two per quarter of the rows, each taking half of the tile's heads: its
+// epilogue is long, and what of it the next tile's products do not hide shows at the end of the kernel.
 template <int BN, bool QKV>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(QKV ? kTcThreads + 128 : kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a, TcQkv qa) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
@@ -200,7 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull0 + 8 * i, 1);
-      mbar_init(tempty0 + 8 * i, 4);        // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * i, QKV ? 8 : 4);        // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -290,10 +322,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int row = m0 + quad * 32 + lane;
       const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
       if constexpr (QKV) {
+        const int c_lo = ((warp - 2) >> 2) * (BN / 2);          // this warp group's half of the tile's columns
         if (qa.head_dim == 128) {
-          for (int c = 0; c < BN; c += 128) qkv_head_epilogue<128>(qa, lane_base + c, row, a.M, (n0 + c) / 128);
+          for (int c = c_lo; c < c_lo + BN / 2; c += 128) qkv_head_epilogue<128>(qa, lane_base + c, row, a.M, (n0 + c) / 128);
         } else {
-          for (int c = 0; c < BN; c += 64) qkv_head_epilogue<64>(qa, lane_base + c, row, a.M, (n0 + c) / 64);
+          for (int c = c_lo; c < c_lo + BN / 2; c += 64) qkv_head_epilogue<64>(qa, lane_base + c, row, a.M, (n0 + c) / 64);
         }
       } else
       for (int c = 0; c < cols_per_tile; c += 32) {
@@ -357,7 +390,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs&
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
   dim3 grid((unsigned)(total < sms ? total : sms));
-  launch_prefetching(gemm_tc_kernel<BN, QKV>, grid, dim3(kTcThreads), (size_t)smem, s, mx, mw, a, qa);
+  launch_prefetching(gemm_tc_kernel<BN, QKV>, grid, dim3(QKV ? kTcThreads + 128 : kTcThreads), (size_t)smem, s, mx, mw, a, qa);
   return check_launch("gemm_tc");
 }
 
@@ -420,8 +453,6 @@ extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int h
               ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
               ((uintptr_t)q_gain % 16 == 0) && ((uintptr_t)k_gain % 16 == 0) && ((uintptr_t)cos_table % 16 == 0) &&
               ((uintptr_t)sin_table % 16 == 0), "gemm_tc_qkv: every tensor must be 16-byte aligned");
-  const long long m_tiles = (M + 127) / 128;
-  const int bn = m_tiles * ((N + 255) / 256) >= 100 ? 256 : 128;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, kTcBM);
   if (rc) return rc;
@@ -435,5 +466,5 @@ extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int h
   qa.tok_seq = tok_seq; qa.tok_pos = tok_pos; qa.block_table = block_table; qa.table_stride = table_stride;
   qa.heads = heads; qa.kv_heads = kv_heads; qa.head_dim = head_dim; qa.eps = eps;
   cudaStream_t s = (cudaStream_t)stream;
-  return bn == 256 ? launch_tc<256, true>(mx, mw, a, s, qa) : launch_tc<128, true>(mx, mw, a, s, qa);
+  return launch_tc<256, true>(mx, mw, a, s, qa);
 }
