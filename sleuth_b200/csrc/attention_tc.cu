@@ -226,13 +226,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!ready && lane == 0) atomicExch(a.status, code);
       return ready;
     };
+    auto wait_warp2 = [&](uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b, int code) -> bool {
+      const bool ready = mbar_wait2(bar_a, parity_a, bar_b, parity_b);
+      if (!ready && lane == 0) atomicExch(a.status, code);
+      return ready;
+    };
     auto arrive_warp = [&](uint32_t bar) {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar);
     };
     for (int j = 0; j < n_pages; ++j) {
       const int b = j & 1, key0 = (page_lo + j) * 64 + half * 32;
-      if (!wait_warp(s_full + 8 * b, (j >> 1) & 1, 28)) { ok = false; break; }
+      // the scores of this page are complete, and the partner has read the maximum of the last page
+      if (j == 0 ? !wait_warp(s_full + 8 * b, (j >> 1) & 1, 28)
+                 : !wait_warp2(s_full + 8 * b, (j >> 1) & 1, xr, (j - 1) & 1, 28)) { ok = false; break; }
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(lane_addr + (uint32_t)(b * 64 + half * 32), sr);
@@ -256,10 +263,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       {
         const uint32_t bits = __float_as_uint(mx);
         const unsigned short up = (unsigned short)(((bits & 0x80000000u) ? bits : bits + 0xffffu) >> 16);
-        if (j > 0 && !wait_warp(xr, (j - 1) & 1, 33)) { ok = false; break; }      // the partner has read the last one
         xch[half * 128 + r] = up;
         arrive_warp(xw);
-        if (!wait_warp(xw, j & 1, 34)) { ok = false; break; }
+        // the partner's maximum is there, and the last product has read P (and its part of O can be rescaled)
+        if (j == 0 ? !wait_warp(xw, j & 1, 34)
+                   : !wait_warp2(xw, j & 1, pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 34)) { ok = false; break; }
         const unsigned short other = xch[(half ^ 1) * 128 + r];
         arrive_warp(xr);
         mx = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
@@ -267,7 +275,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        if (!wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29)) { ok = false; break; }
         tc_fence_after();
         const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
 #pragma unroll
@@ -295,7 +302,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
       }
       l += l0 + l1;
-      if (j > 0 && !wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 30)) { ok = false; break; }     // the last product has read P
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         const uint32_t dst = sP + (uint32_t)(r * 128 + (((half * 4 + ch) ^ (r & 7)) << 4));
@@ -379,7 +385,8 @@ static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   const int G = a.heads / a.kv_heads;
   const int tiles = (max_count * G + kAtRows - 1) / kAtRows;
   dim3 grid(tiles, a.kv_heads, n_seqs);
-  launch(attn_tc_kernel<HD>, grid, dim3(kAtThreads), (size_t)L::TOTAL, s, mq, mk, mv, a);
+  // its prologue (barriers, tensor memory) runs while the kernel in front drains
+  launch_prefetching(attn_tc_kernel<HD>, grid, dim3(kAtThreads), (size_t)L::TOTAL, s, mq, mk, mv, a);
   return check_launch("attention (tcgen05)");
 }
 

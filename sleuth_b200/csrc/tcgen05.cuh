@@ -32,6 +32,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// Waits for two barriers at once: both are polled in every round, so their latencies overlap.
+__device__ __forceinline__ bool mbar_wait2(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b) {
+  uint32_t done_a = 0, done_b = 0;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok_a = 1, ok_b = 1;
+    if (!done_a)
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok_a) : "r"(bar_a), "r"(parity_a) : "memory");
+    if (!done_b)
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok_b) : "r"(bar_b), "r"(parity_b) : "memory");
+    done_a |= ok_a;
+    done_b |= ok_b;
+    if (done_a && done_b) return true;
+  }
+  return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
