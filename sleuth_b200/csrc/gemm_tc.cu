@@ -25,7 +25,12 @@ namespace slb {
 
 constexpr int kTcBM = 128;
 constexpr int kTcBK = 64;             // bf16 elements per slice: 128 bytes, one swizzle row
-constexpr int kTcStages = 4;
+// TMA stages: as many as fit in 192 KB (at most 8). What is in flight per SM bounds the operand stream (latency x
+// bandwidth), so narrow tiles, whose stages are small, get more of them.
+constexpr int tc_stages(int bn) {
+  const int n = (192 * 1024) / ((kTcBM + bn) * kTcBK * 2);
+  return n > 8 ? 8 : n;
+}
 constexpr int kTcThreads = 192;       // producer warp, MMA warp, four epilogue warps
 
 enum TcMode : int { kTcBf16 = 0, kTcF32 = 1, kTcAddF32 = 2, kTcSwiglu = 3, kTcQkv = 4 };
@@ -212,7 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2, STAGE = A_BYTES + B_BYTES;
-  constexpr int S = kTcStages;
+  constexpr int S = tc_stages(BN);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * STAGE);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * S, tfull0 = empty0 + 8 * S, tempty0 = tfull0 + 16;
@@ -278,6 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       constexpr uint32_t idesc = instr_desc(kTcBM, BN);
       int it = 0, t = 0;
       bool ok = true;
+      uint32_t next_ready = 0;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
         const int buf = t & 1;
         if (t >= 2 && !mbar_wait(tempty0 + 8 * buf, ((t / 2) - 1) & 1)) {      // the epilogue has drained this accumulator
@@ -288,12 +294,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const uint32_t acc = tmem + (uint32_t)(buf * BN);
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % S;
-          if (!mbar_wait(full0 + 8 * s, (it / S) & 1)) {
+          if (!next_ready && !mbar_wait(full0 + 8 * s, (it / S) & 1)) {
             atomicExch(a.status, 2);
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // A look at the next stage's barrier goes out before this stage's products: its answer (a couple of
+          // hundred cycles away) is back by the time they are issued, so a loaded stage costs no wait of its own.
+          const int sn = (it + 1) % S;
+          next_ready = mbar_test(full0 + 8 * sn, ((it + 1) / S) & 1);
           const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
           const uint64_t da = smem_desc(sa), db = smem_desc(sb);
 #pragma unroll
@@ -374,7 +384,8 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 template <int BN, bool QKV = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s, const TcQkv& qa = TcQkv{}) {
-  const int smem = kTcStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kTcStages + 4) * 8 + 16 + 1024;
+  constexpr int kStages = tc_stages(BN);
+  const int smem = kStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kStages + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
