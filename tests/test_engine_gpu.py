@@ -234,7 +234,9 @@ def test_sampler_against_the_plain_pipeline(vocab):
     cases = [SamplingConfig(temperature=0.0), SamplingConfig(temperature=0.7), SamplingConfig(temperature=1.3, top_k=40),
              SamplingConfig(temperature=1.0, top_p=0.8), SamplingConfig(temperature=1.1, min_p=0.05),
              SamplingConfig(temperature=0.9, top_k=200, top_p=0.9, min_p=0.02, repetition_penalty=1.3),
-             SamplingConfig(temperature=0.0, repetition_penalty=1.5)]
+             SamplingConfig(temperature=0.0, repetition_penalty=1.5),
+             # more survivors of top-k than the kernel keeps in shared memory: it goes on over the whole row
+             SamplingConfig(temperature=0.8, top_k=5000, top_p=0.95), SamplingConfig(temperature=1.2, top_k=3000)]
     recent = [[int(logits[r].argmax()), 3, 7] for r in range(rows)]
     banned = [[int(logits[r].topk(2).indices[1])] if r % 2 else [] for r in range(rows)]
     for ci, cfg in enumerate(cases):
@@ -252,6 +254,30 @@ def test_sampler_against_the_plain_pipeline(vocab):
                     cdf = p.cumsum(-1)
                     edge = min(abs(float(cdf[want]) - float(u[r])), abs(float(cdf[want] - p[want]) - float(u[r])))
                     assert not cfg.greedy and edge < 1e-5 and float(p[got[r]]) > 0, (ci, trial, r, got[r], want)
+
+
+def test_sampler_keeps_values_tied_with_the_kth(vocab=40000):
+    """Logits on a coarse grid tie by the hundred; top-k keeps every value equal to the k-th (`x < kth` goes), a
+    temperature that is no power of two must not split such a tie, and the draw still follows token order."""
+    from sleuth_b200.sampling import SamplingConfig
+    from sleuth_b200.sampling.sampler import Sampler
+    g = torch.Generator().manual_seed(5)
+    rows = 4
+    logits = (torch.randn(rows, vocab, generator=g) * 3).mul(4).round().div(4)
+    sampler = Sampler("cuda:0", vocab)
+    for cfg in (SamplingConfig(temperature=0.7, top_k=50), SamplingConfig(temperature=1.3, top_k=3000),
+                SamplingConfig(temperature=3.0, top_k=1, min_p=0.0)):
+        for trial in range(3):
+            u = torch.rand(rows, generator=g).clamp(0, 0.999999)
+            got = sampler.to_host(sampler.choose(logits.clone().to("cuda:0"), cfg, u.numpy()))
+            for r in range(rows):
+                final = plain.final_logits(logits[r], cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p)
+                want = plain.draw(final, float(u[r]))
+                if got[r] != want:
+                    p = final.double().softmax(-1)
+                    cdf = p.cumsum(-1)
+                    edge = min(abs(float(cdf[want]) - float(u[r])), abs(float(cdf[want] - p[want]) - float(u[r])))
+                    assert edge < 1e-5 and float(p[got[r]]) > 0, (cfg, trial, r, got[r], want)
 
 
 def test_missing_weights_are_reported_at_load(model_folders, tmp_path):
