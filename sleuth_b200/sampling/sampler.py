@@ -56,9 +56,29 @@ class Sampler:
             if uniform is None:
                 raise ValueError("sampling with a temperature needs one uniform number per row")
             if not isinstance(uniform, torch.Tensor):
-                uniform = torch.as_tensor(np.asarray(uniform, dtype=np.float32)).to(self.device)
+                uniform = self._upload(np.asarray(uniform, dtype=np.float32))
             ops.sample(logits, limit, cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p, uniform, out, stream)
         return out
+
+    def _upload(self, values: np.ndarray) -> torch.Tensor:
+        """The uniform numbers of a step on the device, through one of four pinned buffers: the copy is asynchronous,
+        so a loop that runs ahead of the GPU is not held up; a buffer is reused only when its last copy is done."""
+        n = values.size
+        if not hasattr(self, "_u_ring") or self._u_ring[0][0].numel() < n:
+            cap = max(1024, 2 * n)
+            self._u_ring = [(torch.zeros(cap, dtype=torch.float32).pin_memory(),
+                             torch.zeros(cap, dtype=torch.float32, device=self.device), torch.cuda.Event())
+                            for _ in range(4)]
+            self._u_turn, self._u_used = 0, [False] * 4
+        host, dev, ev = self._u_ring[self._u_turn]
+        if self._u_used[self._u_turn]:
+            ev.synchronize()
+        host[:n].copy_(torch.from_numpy(values.reshape(-1)))
+        dev[:n].copy_(host[:n], non_blocking=True)
+        ev.record(torch.cuda.current_stream(self.device))
+        self._u_used[self._u_turn] = True
+        self._u_turn = (self._u_turn + 1) % 4
+        return dev[:n]
 
     def to_host(self, tokens: torch.Tensor) -> list[int]:
         n = tokens.numel()
