@@ -24,6 +24,7 @@ from ..cache.paged import PagedCache
 from ..config.base import read_config_json
 from ..config.registry import parse_config
 from ..parts.base import BuildContext
+from ..kernels import ops
 from ..sampling.config import SamplingConfig
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_into
@@ -195,6 +196,9 @@ class Engine:
                                        max_batch)
         finally:
             self.stepper.use_graphs = before
+        # every token has been read back, so the device is idle: one look at the status word that the tensor-memory
+        # kernels write when a bounded wait gives up (their results would be wrong, and nothing else would say so)
+        ops.gemm_tc_check(self.device)
         for r in results:
             r.stats.update(kv_cache_mb=round(self.cache.nbytes() / 1e6, 2), device=str(self.device),
                            dtype=str(self.dtype).replace("torch.", ""))

@@ -41,6 +41,7 @@ def main(argv=None) -> int:
 
     from .config.base import read_config_json
     from .engine.engine import Engine
+    from .kernels import ops
     from .engine.stepper import StepEntry
 
     if a.max_tokens <= 0:
@@ -72,6 +73,7 @@ def main(argv=None) -> int:
                     f.write(host.astype("<f4", copy=False).tobytes())
             else:
                 torch.cuda.synchronize()
+            ops.gemm_tc_check(engine.device)     # the step is complete: did a tensor-memory kernel give up a wait?
         ended = [str(r) for r in msg.get("end", [])]
         if ended:
             engine.close([slot_of.pop(r) for r in ended if r in slot_of])
