@@ -29,6 +29,8 @@ class Model:
         self.head = LMHead(spec.head, ctx)
         self.hidden = spec.embedding.dim
         self.vocab = spec.head.vocab
+        # single-token steps are recorded as CUDA graphs only if every layer allows it
+        self.capturable = all(getattr(layer, "capturable", True) for layer in self.layers)
         # cache entries: the first application that names an entry owns it
         self.entry_owner: dict[int, int] = {}
         for i, e in enumerate(spec.schedule):

@@ -205,7 +205,8 @@ class Stepper:
         if graph is not None:
             graph.replay()
             self.graph_kernel_launches += self._graph_own[gkey]
-        elif self.use_graphs and n <= self.max_graph_batch and gkey in self._seen_decode:
+        elif (self.use_graphs and getattr(self.model, "capturable", True) and n <= self.max_graph_batch
+              and gkey in self._seen_decode):
             before = ops.lib().launches
             self._graphs[gkey] = self._capture(b, logits)
             self._graph_own[gkey] = ops.lib().launches - before

@@ -25,6 +25,9 @@ on the fast path), ``"vector"`` (gains, biases) in float32, ``"table"`` (integer
 A tensor that the file stores in 32-bit is never narrowed on the way in; a matrix product that
 runs in bfloat16 makes its own bfloat16 copy of such a matrix.
 
+A part whose ``forward`` must run afresh every step (it reads the step's host-side values, or its launches
+depend on the data) sets ``capturable = False``; single-token steps are then not recorded as CUDA graphs.
+
 New kinds are added with ``register_norm``, ``register_position``, ``register_mixer``,
 ``register_ffn``, ``register_layer``; a spec's ``kind`` selects the class.
 """
@@ -75,6 +78,10 @@ class Normed:
 
 class Part:
     accepts_normed = False      # True: ``forward`` takes a ``Normed`` instead of the normalised tensor
+    # False: ``forward`` cannot be recorded once and replayed, because it reads host-side values of the step
+    # (``b.host_slots``, ``b.host_counts``), waits for the device, or launches work whose shape depends on the data
+    # (routing). A model with such a part runs its single-token steps launch by launch instead of as a CUDA graph.
+    capturable = True
 
     def declare(self) -> dict[str, ParamDecl]:
         return {}

@@ -19,6 +19,7 @@ class PreNormLayer(Part):
         self.norm2 = build_norm(spec.norm2, ctx)
         self.ffn = build_ffn(spec.ffn, ctx)
         self.children = {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn}
+        self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
 
     def declare(self):
         out = {}

@@ -1,7 +1,8 @@
 """The framework's generality, shown with toy parts that exist only here: a mixer with per-sequence
-state of its own, a layer named twice in the schedule, and a layer that reads another layer's cache.
-They are registered, built, loaded and stepped through the public registries without touching a
-file of the package."""
+state of its own, a layer named twice in the schedule, a layer that reads another layer's cache, a
+feed-forward that routes every token to one of three experts, and another position encoding (positions
+scaled down, only half of each head rotated). They are registered, built, loaded and stepped through the
+public registries without touching a file of the package."""
 
 from __future__ import annotations
 
@@ -33,6 +34,26 @@ class RunningMeanSpec:
     kind: str = "running_mean"
 
 
+@dataclass(frozen=True)
+class Top1ExpertsSpec:
+    hidden: int
+    inner: int
+    experts: int
+    kind: str = "top1_experts"
+
+
+@dataclass(frozen=True)
+class ScaledRotarySpec:
+    head_dim: int
+    theta: float
+    factor: float
+    rotary_dim: int
+    kind: str = "scaled_rotary"
+
+
+EXPERTS, EXPERT_INNER, POS_FACTOR, ROT = 3, 40, 4.0, 8
+
+
 def toy_spec(cfg: ToyConfig, tensor_names=None):
     from sleuth_b200.parts.spec import (AttentionSpec, EmbeddingSpec, GatedMLPSpec, HeadSpec, LayerSpec, ModelSpec,
                                         NormSpec, PositionSpec, ScheduleEntry)
@@ -52,7 +73,22 @@ def toy_spec(cfg: ToyConfig, tensor_names=None):
     attn_names.update({"q_norm.weight": "self_attn.q_norm.weight", "k_norm.weight": "self_attn.k_norm.weight"})
     attn = AttentionSpec(hidden=d, heads=HEADS, kv_heads=KVH, head_dim=HD, position=pos, qk_norm=True, qk_norm_eps=EPS)
     layer0 = LayerSpec(mixer=attn, ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS), names=names(0, attn_names))
-    if cfg.variant == "state":
+    if cfg.variant == "routed":
+        # layer 0 rotates with the toy position encoding, layer 1 routes its feed-forward; both are toy kinds
+        attn0 = AttentionSpec(hidden=d, heads=HEADS, kv_heads=KVH, head_dim=HD, qk_norm=True, qk_norm_eps=EPS,
+                              position=ScaledRotarySpec(head_dim=HD, theta=THETA, factor=POS_FACTOR, rotary_dim=ROT))
+        layer0 = LayerSpec(mixer=attn0, ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS), names=names(0, attn_names))
+        n1 = names(1, attn_names)
+        for k in [k for k in n1 if k.startswith("ffn.")]:
+            del n1[k]
+        n1["ffn.router.weight"] = "model.layers.1.moe.router.weight"
+        for e in range(EXPERTS):
+            n1[f"ffn.experts.{e}.up.weight"] = f"model.layers.1.moe.experts.{e}.up.weight"
+            n1[f"ffn.experts.{e}.down.weight"] = f"model.layers.1.moe.experts.{e}.down.weight"
+        layer1 = LayerSpec(mixer=attn, ffn=Top1ExpertsSpec(d, EXPERT_INNER, EXPERTS), norm1=NormSpec(d, EPS),
+                           norm2=NormSpec(d, EPS), names=n1)
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1))
+    elif cfg.variant == "state":
         layer1 = LayerSpec(mixer=RunningMeanSpec(d), ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS),
                            names=names(1, {"w.weight": "mean_mixer.w.weight"}))
         schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2))      # layer 0 runs twice
@@ -74,6 +110,7 @@ def make_running_mean_mixer():
     class RunningMean(Part):
         """out[t] = W @ mean(h[0..t]) of the token's own sequence. The sum so far and the count are the
         sequence's state, kept in the cache's state region under the sequence's slot."""
+        capturable = False      # it walks the step's sequences on the host
 
         def __init__(self, spec, ctx):
             self.hidden, self.ctx = spec.hidden, ctx
@@ -102,15 +139,74 @@ def make_running_mean_mixer():
     return RunningMean
 
 
+def make_top1_experts():
+    from sleuth_b200.parts.base import ParamDecl, Part
+
+    class Top1Experts(Part):
+        """Every token goes to the expert with the largest router logit (float32, first index on ties); the
+        expert's output (relu MLP) is weighted by that expert's softmax probability and added to the stream."""
+        capturable = False      # which rows go to which expert is read back on the host
+
+        def __init__(self, spec, ctx):
+            self.spec = spec
+
+        def declare(self):
+            s = self.spec
+            d = {"router.weight": ParamDecl((s.experts, s.hidden))}
+            for e in range(s.experts):
+                d[f"experts.{e}.up.weight"] = ParamDecl((s.inner, s.hidden))
+                d[f"experts.{e}.down.weight"] = ParamDecl((s.hidden, s.inner))
+            return d
+
+        def bind(self, t):
+            self.router = t["router.weight"].float()
+            self.up = [t[f"experts.{e}.up.weight"].float() for e in range(self.spec.experts)]
+            self.down = [t[f"experts.{e}.down.weight"].float() for e in range(self.spec.experts)]
+
+        def forward(self, h, x, b, ws):
+            hf = h.float()
+            prob = (hf @ self.router.T).softmax(-1)
+            chosen = prob.argmax(-1)
+            for e in range(self.spec.experts):
+                rows = (chosen == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(hf[rows] @ self.up[e].T) @ self.down[e].T
+                    x.index_add_(0, rows, y * prob[rows, e][:, None])
+
+    return Top1Experts
+
+
+def make_scaled_rotary():
+    from sleuth_b200.parts.base import Part
+
+    class ScaledRotary(Part):
+        """Rotate-half over the first ``rotary_dim`` channels of a head, by the angle (position / factor) * frequency."""
+
+        def __init__(self, spec, ctx):
+            self.rot_dim = spec.rotary_dim
+            inv = 1.0 / (spec.theta ** (torch.arange(0, self.rot_dim, 2, dtype=torch.float32) / self.rot_dim))
+            ang = torch.outer(torch.arange(ctx.max_positions, dtype=torch.float32) / spec.factor, inv)
+            self.cos, self.sin = ang.cos().contiguous().to(ctx.device), ang.sin().contiguous().to(ctx.device)
+
+        def tables(self):
+            return self.cos, self.sin
+
+    return ScaledRotary
+
+
 @pytest.fixture()
 def toy_registered():
     from sleuth_b200.config import register_architecture, unregister_architecture
-    from sleuth_b200.parts import register_mixer, unregister
+    from sleuth_b200.parts import register_ffn, register_mixer, register_position, unregister
     register_mixer("running_mean", make_running_mean_mixer())
+    register_ffn("top1_experts", make_top1_experts())
+    register_position("scaled_rotary", make_scaled_rotary())
     register_architecture("ToyForCausalLM", ToyConfig, toy_spec, model_types=("toy",))
     yield
     unregister_architecture("ToyForCausalLM")
     unregister("mixer", "running_mean")
+    unregister("ffn", "top1_experts")
+    unregister("position", "scaled_rotary")
 
 
 def settings():
@@ -155,7 +251,48 @@ def plain_shared_kv_model(w, ids):
     return plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T
 
 
-@pytest.mark.parametrize("variant,oracle", [("state", plain_state_model), ("shared_kv", plain_shared_kv_model)])
+def plain_routed_model(w, ids):
+    s = settings()
+    w = {k: v.float() for k, v in w.items()}
+    T = len(ids)
+    x = w["model.embed_tokens.weight"][torch.as_tensor(ids)]
+    # layer 0 by hand: its rotation is the toy one (scaled positions, the first ROT channels of a head only)
+    inv = 1.0 / (THETA ** (torch.arange(0, ROT, 2, dtype=torch.float32) / ROT))
+    ang = torch.outer(torch.arange(T, dtype=torch.float32) / POS_FACTOR, inv)
+
+    def rotate(v):       # [heads, T, HD]
+        a, b, rest = v[..., :ROT // 2], v[..., ROT // 2:ROT], v[..., ROT:]
+        return torch.cat([a * ang.cos() - b * ang.sin(), b * ang.cos() + a * ang.sin(), rest], dim=-1)
+
+    p = "model.layers.0.self_attn."
+    h = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], EPS)
+    q = (h @ w[p + "q_proj.weight"].T).view(T, HEADS, HD).transpose(0, 1)
+    k = (h @ w[p + "k_proj.weight"].T).view(T, KVH, HD).transpose(0, 1)
+    v = (h @ w[p + "v_proj.weight"].T).view(T, KVH, HD).transpose(0, 1)
+    q = rotate(plain.rms_norm(q, w[p + "q_norm.weight"], EPS))
+    k = rotate(plain.rms_norm(k, w[p + "k_norm.weight"], EPS))
+    kk, vv = k.repeat_interleave(HEADS // KVH, 0), v.repeat_interleave(HEADS // KVH, 0)
+    sc = ((q @ kk.transpose(-2, -1)) / math.sqrt(HD)).masked_fill(~plain.causal_mask(T, 0), float("-inf"))
+    x = x + (sc.softmax(-1) @ vv).transpose(0, 1).reshape(T, HEADS * HD) @ w[p + "o_proj.weight"].T
+    x = x + plain.swiglu(plain.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], EPS), w, "model.layers.0.mlp.")
+    # layer 1: ordinary attention, then the routed feed-forward
+    cos, sin = plain.rope_tables(HD, T, THETA)
+    h = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], EPS)
+    x = x + plain.attention(h, w, "model.layers.1.self_attn.", s, 0, cos, sin)
+    h = plain.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], EPS)
+    prob = (h @ w["model.layers.1.moe.router.weight"].T).softmax(-1)
+    chosen = prob.argmax(-1)
+    y = torch.zeros_like(x)
+    for t in range(T):
+        e = int(chosen[t])
+        y[t] = (torch.relu(h[t] @ w[f"model.layers.1.moe.experts.{e}.up.weight"].T)
+                @ w[f"model.layers.1.moe.experts.{e}.down.weight"].T) * prob[t, e]
+    x = x + y
+    return plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("variant,oracle", [("state", plain_state_model), ("shared_kv", plain_shared_kv_model),
+                                            ("routed", plain_routed_model)])
 def test_toy_architecture_builds_loads_and_steps(variant, oracle, toy_registered, tmp_path):
     import sleuth_b200 as sb
     from sleuth_b200.cache.paged import KVRequest, StateRequest
@@ -167,6 +304,9 @@ def test_toy_architecture_builds_loads_and_steps(variant, oracle, toy_registered
     if variant == "state":
         assert "model.layers.1.mean_mixer.w.weight" in w
         assert [type(r) for r in reqs] == [KVRequest, StateRequest, KVRequest]          # the repeated layer has two entries
+    elif variant == "routed":
+        assert "model.layers.1.moe.experts.2.down.weight" in w and "model.layers.1.mlp.gate_proj.weight" not in w
+        assert [type(r) for r in reqs] == [KVRequest, KVRequest]
     else:
         assert "model.layers.1.self_attn.k_proj.weight" not in w and len(reqs) == 1     # one entry, written by layer 0
     rng = np.random.default_rng(1)
@@ -184,3 +324,5 @@ def test_toy_architecture_builds_loads_and_steps(variant, oracle, toy_registered
     eng.close([slot])
     res = eng.generate([a[:5], b], max_new_tokens=4, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())
     assert res[0].new_ids[0] == int(oracle(w, a[:5])[-1].argmax())
+    # parts that walk the step on the host or route by data are not recorded: no CUDA graph was made of a step
+    assert eng.model.capturable == (variant == "shared_kv") and (variant == "shared_kv" or not eng.stepper._graphs)
