@@ -278,41 +278,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer ----
-      constexpr uint32_t idesc = instr_desc(kTcBM, BN);
-      int it = 0, t = 0;
-      bool ok = true;
-      uint32_t next_ready = 0;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
-        const int buf = t & 1;
-        if (t >= 2 && !mbar_wait(tempty0 + 8 * buf, ((t / 2) - 1) & 1)) {      // the epilogue has drained this accumulator
-          atomicExch(a.status, 4);
+    // ---- MMA issuer: the whole warp walks the loop (its counters and descriptors then live in uniform registers),
+    // one lane issues the products and the commits ----
+    constexpr uint32_t idesc = instr_desc(kTcBM, BN);
+    constexpr uint32_t kAll = 0xffffffffu;
+    int it = 0, t = 0;
+    bool ok = true;
+    bool next_ready = false;
+    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      if (t >= 2 && !__all_sync(kAll, mbar_wait(tempty0 + 8 * buf, ((t / 2) - 1) & 1))) {   // the epilogue has drained this accumulator
+        if (lane == 0) atomicExch(a.status, 4);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = tmem + (uint32_t)(buf * BN);
+      for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        const int s = it % S;
+        if (!next_ready && !__all_sync(kAll, mbar_wait(full0 + 8 * s, (it / S) & 1))) {
+          if (lane == 0) atomicExch(a.status, 2);
+          ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem + (uint32_t)(buf * BN);
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-          const int s = it % S;
-          if (!next_ready && !mbar_wait(full0 + 8 * s, (it / S) & 1)) {
-            atomicExch(a.status, 2);
-            ok = false;
-            break;
-          }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          // A look at the next stage's barrier goes out before this stage's products: its answer (a couple of
-          // hundred cycles away) is back by the time they are issued, so a loaded stage costs no wait of its own.
-          const int sn = (it + 1) % S;
-          next_ready = mbar_test(full0 + 8 * sn, ((it + 1) / S) & 1);
-          const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
-          const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+        // A look at the next stage's barrier goes out before this stage's products: its answer (a couple of
+        // hundred cycles away) is back by the time they are issued, so a loaded stage costs no wait of its own.
+        const int sn = (it + 1) % S;
+        const uint32_t probe = mbar_test(full0 + 8 * sn, ((it + 1) / S) & 1);
+        const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
+        const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+        if (lane == 0) {
 #pragma unroll
           for (int k4 = 0; k4 < kTcBK / 16; ++k4)    // 16 elements = 32 bytes further along K inside the swizzle row
             mma_bf16_ss(acc, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
           mma_commit(empty0 + 8 * s);                // fires when these MMAs have read the stage
         }
-        if (ok) mma_commit(tfull0 + 8 * buf);        // fires when the whole tile has been accumulated
+        next_ready = __all_sync(kAll, probe != 0);
       }
+      if (ok && lane == 0) mma_commit(tfull0 + 8 * buf);        // fires when the whole tile has been accumulated
+      __syncwarp();
     }
   } else {
     // ---- epilogue: warps 2..5, tensor-memory lanes 32 * (warp % 4) .. + 31 ----
