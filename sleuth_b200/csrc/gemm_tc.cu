@@ -325,6 +325,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++t) {
       const int buf = t & 1;
       const int m0 = (tile % m_tiles) * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+      const int row = m0 + quad * 32 + lane;
+      // Adding into the stream: the old values of this thread's row are fetched while the products still run, so
+      // that the epilogue (which nothing hides when a block has a single tile) does not wait for them.
+      constexpr bool kPreload = !QKV && BN <= 128;
+      float old[kPreload ? BN : 1];
+      // (the whole warp or none of it: the tensor-memory loads are collective; a warp with rows beyond the matrix
+      // takes the general path)
+      const bool preloaded = kPreload && __all_sync(0xffffffffu, a.mode == kTcAddF32 && row < a.M && n0 + BN <= a.N &&
+                                                                    (a.ldc % 4 == 0));
+      if constexpr (kPreload) {
+        if (preloaded) {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.C) + (size_t)row * a.ldc + n0);
+#pragma unroll
+          for (int j = 0; j < BN / 4; ++j) {
+            const float4 o = src[j];
+            old[4 * j] = o.x; old[4 * j + 1] = o.y; old[4 * j + 2] = o.z; old[4 * j + 3] = o.w;
+          }
+        }
+      }
       bool ready = true;
       if (lane == 0) ready = mbar_wait(tfull0 + 8 * buf, (t / 2) & 1);
       ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
@@ -333,8 +352,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = m0 + quad * 32 + lane;
       const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+      if constexpr (kPreload) {
+        if (preloaded) {
+          float* dst = reinterpret_cast<float*>(a.C) + (size_t)row * a.ldc + n0;
+#pragma unroll
+          for (int c = 0; c < BN; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + c, r);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(dst + c + j) =
+                  make_float4(old[c + j] + __uint_as_float(r[j]), old[c + j + 1] + __uint_as_float(r[j + 1]),
+                              old[c + j + 2] + __uint_as_float(r[j + 2]), old[c + j + 3] + __uint_as_float(r[j + 3]));
+          }
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+          continue;
+        }
+      }
       if constexpr (QKV) {
         const int c_lo = ((warp - 2) >> 2) * (BN / 2);          // this warp group's half of the tile's columns
         if (qa.head_dim == 128) {
