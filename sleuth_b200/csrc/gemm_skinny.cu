@@ -116,6 +116,19 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   pdl_launch_dependents();
   fetch_weights(kb_begin);
   pdl_wait();
+  // Adding into the stream: the old values of the outputs this thread will write are asked for now, so that the
+  // epilogue does not end on a load from L2.
+  constexpr int kOutPerThread = (16 * MT * NF * 8 + kSkinnyWarps * 32 - 1) / (kSkinnyWarps * 32);
+  float old_out[kOutPerThread];
+  if (MODE == kAddF32) {
+#pragma unroll
+    for (int i = 0; i < kOutPerThread; ++i) {
+      const int idx = threadIdx.x + i * kSkinnyWarps * 32;
+      const int r = idx / (NF * 8), feat = n0 + idx % (NF * 8);
+      old_out[i] = (idx < 16 * MT * NF * 8 && r < a.M && feat < a.N)
+                       ? reinterpret_cast<const float*>(a.C)[(size_t)r * a.ldc + feat] : 0.0f;
+    }
+  }
   float ssq0 = 0.0f, ssq1 = 0.0f;     // NORM: sums of squares of this lane's share of rows g and g + 8
   for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
     if (kb != kb_begin) fetch_weights(kb);
@@ -202,7 +215,10 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   }
   __syncthreads();
 
-  for (int idx = threadIdx.x; idx < 16 * MT * NF * 8; idx += kSkinnyWarps * 32) {
+#pragma unroll
+  for (int i = 0; i < kOutPerThread; ++i) {
+    const int idx = threadIdx.x + i * kSkinnyWarps * 32;
+    if (idx >= 16 * MT * NF * 8) break;
     const int r = idx / (NF * 8), c = idx % (NF * 8);
     const int feat = n0 + c;
     if (r >= a.M || feat >= a.N) continue;
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
     } else if (MODE == kStoreF32) {
       reinterpret_cast<float*>(a.C)[(size_t)r * a.ldc + feat] = v;
     } else {
-      reinterpret_cast<float*>(a.C)[(size_t)r * a.ldc + feat] += v;
+      reinterpret_cast<float*>(a.C)[(size_t)r * a.ldc + feat] = old_out[i] + v;
     }
   }
 }
