@@ -14,7 +14,8 @@
 //   * warp 1, one lane: the values. It asks TMA for the value pages and issues O += P V (M = 128, N = HD) as soon as
 //     the softmax has written P into shared memory; V is read in place as an N-major operand.
 //   * warps 2 to 9: softmax, two threads per row (keys 0..31 and 32..63 of the page). They read their half of a score
-//     row from tensor memory, mask it, agree on the row's maximum through shared memory, write P as bfloat16 into
+//     row from tensor memory, mask it, agree on the row's maximum through shared memory (the two warps of a row
+//     meet at a hardware barrier of their own, twice per page), write P as bfloat16 into
 //     shared memory, and when a row's maximum has grown by more than 2^8 since O was last scaled, rescale O in
 //     tensor memory (otherwise the old maximum keeps serving: exact, since numerator and denominator carry the
 //     same factor). At the end they add their sums, divide and store. Value rows of the last page that lie beyond
@@ -24,8 +25,9 @@
 // softmax the other's products keep the tensor core busy. A block's own chain per page (scores -> softmax -> P ->
 // product) is what bounds a single long prompt; many sequences or heads fill the GPU.
 //
-// Every wait is bounded; a wait that gives up writes a code into `status`, and the block still frees its tensor
-// memory and returns. TMA loads never use cluster multicast.
+// Every wait on an mbarrier is bounded; a wait that gives up writes a code into `status`, the thread stops waiting
+// and runs on to the end of its loop (so that it still meets its partner at their hardware barrier), and the block
+// frees its tensor memory and returns. TMA loads never use cluster multicast.
 #include <math.h>
 
 #include "tcgen05.cuh"
@@ -69,7 +71,7 @@ struct AttnTcLayout {
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES; // two stages
   static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
   static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  static constexpr int N_BARS = 20;
+  static constexpr int N_BARS = 12;
   static constexpr int XCH_OFF = BAR_OFF + N_BARS * 8 + 16;   // row maxima as 16-bit values, [2 halves][128 rows]
   static constexpr int TOTAL = XCH_OFF + 2 * kAtRows * 2;
   static_assert(2 * (TOTAL + 1024) <= 228 * 1024, "two blocks must fit on an SM");
@@ -91,7 +93,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t sQ = base + L::Q_OFF, sK = base + L::K_OFF, sV = base + L::V_OFF, sP = base + L::P_OFF;
   const uint32_t bars = base + L::BAR_OFF;
   const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, s_full = bars + 40, s_empty = bars + 56,
-                 pv_done = bars + 72, p_full = bars + 88, xw_bar = bars + 96, xr_bar = bars + 128;
+                 pv_done = bars + 72, p_full = bars + 88;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + L::N_BARS * 8);
 
   const int seq = blockIdx.z, kh = blockIdx.y;
@@ -118,10 +120,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(s_full + 8 * i, 1);
       mbar_init(pv_done + 8 * i, 1);
       mbar_init(s_empty + 8 * i, 8);     // one arrival per softmax warp
-    }
-    for (int i = 0; i < 4; ++i) {          // the two warps that share a quarter of the rows
-      mbar_init(xw_bar + 8 * i, 2);
-      mbar_init(xr_bar + 8 * i, 2);
     }
     mbar_init(p_full, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -217,29 +215,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int pos = R < rows_total ? past + R / G : -1;        // -1: a padding row sees nothing
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    const uint32_t xw = xw_bar + 8 * quad, xr = xr_bar + 8 * quad;
     unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 halves][128 rows]
     float m_used = -INFINITY, l = 0.0f;
+    // A wait that gives up ends nothing here: the warp notes it, stops waiting and walks on to the end, because its
+    // partner (the warp with the other half of the same rows) meets it at a hardware barrier twice per page and
+    // would otherwise stay there. The result is then garbage and the status word says so.
     bool ok = true;
-    auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) -> bool {
-      const bool ready = mbar_wait(bar, parity);       // every lane polls: no divergence, no shuffle
-      if (!ready && lane == 0) atomicExch(a.status, code);
-      return ready;
-    };
-    auto wait_warp2 = [&](uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b, int code) -> bool {
-      const bool ready = mbar_wait2(bar_a, parity_a, bar_b, parity_b);
-      if (!ready && lane == 0) atomicExch(a.status, code);
-      return ready;
+    auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
+      if (ok && !mbar_wait(bar, parity)) {       // every lane polls: no divergence, no shuffle
+        ok = false;
+        if (lane == 0) atomicExch(a.status, code);
+      }
     };
     auto arrive_warp = [&](uint32_t bar) {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar);
     };
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
+    uint32_t s_ready = 0;
     for (int j = 0; j < n_pages; ++j) {
       const int b = j & 1, key0 = (page_lo + j) * 64 + half * 32;
-      // the scores of this page are complete, and the partner has read the maximum of the last page
-      if (j == 0 ? !wait_warp(s_full + 8 * b, (j >> 1) & 1, 28)
-                 : !wait_warp2(s_full + 8 * b, (j >> 1) & 1, xr, (j - 1) & 1, 28)) { ok = false; break; }
+      if (!s_ready) wait_warp(s_full + 8 * b, (j >> 1) & 1, 28);
+      // asked now, needed after the maximum: has the last product finished (P free, O complete)?
+      const uint32_t pv_ready = j > 0 ? mbar_test(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1) : 1u;
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(lane_addr + (uint32_t)(b * 64 + half * 32), sr);
@@ -263,15 +261,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       {
         const uint32_t bits = __float_as_uint(mx);
         const unsigned short up = (unsigned short)(((bits & 0x80000000u) ? bits : bits + 0xffffu) >> 16);
+        if (j > 0) pair_sync();            // the partner has read the maximum of the last page
         xch[half * 128 + r] = up;
-        arrive_warp(xw);
-        // the partner's maximum is there, and the last product has read P (and its part of O can be rescaled)
-        if (j == 0 ? !wait_warp(xw, j & 1, 34)
-                   : !wait_warp2(xw, j & 1, pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 34)) { ok = false; break; }
+        pair_sync();
         const unsigned short other = xch[(half ^ 1) * 128 + r];
-        arrive_warp(xr);
         mx = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
       }
+      if (!pv_ready) wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29);
       const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -302,6 +298,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
       }
       l += l0 + l1;
+      // asked now, needed at the top of the next page: are its scores complete?
+      s_ready = j + 1 < n_pages ? mbar_test(s_full + 8 * (b ^ 1), ((j + 1) >> 1) & 1) : 0u;
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         const uint32_t dst = sP + (uint32_t)(r * 128 + (((half * 4 + ch) ^ (r & 7)) << 4));
@@ -310,7 +308,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       const int valid = seq_len - (page_lo + j) * 64;          // rows of this page that belong to the sequence
       if (valid < 64) {
-        if (!wait_warp(v_full + 8 * b, (j >> 1) & 1, 31)) { ok = false; break; }
+        wait_warp(v_full + 8 * b, (j >> 1) & 1, 31);
         if (r < 64 && r >= valid && half < HD / 64) {          // each half clears one 64-wide slab of the row
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
@@ -322,13 +320,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       fence_smem_to_async();
       arrive_warp(p_full);
     }
-    if (ok && wait_warp(pv_done + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, 32)) {
+    wait_warp(pv_done + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, 32);
+    {
       tc_fence_after();
       // the row's sum is the two halves' sums; they meet in the P tile, which the last product has finished reading
       float* xl = reinterpret_cast<float*>(smem + L::P_OFF);
       xl[half * 128 + r] = l;
-      arrive_warp(xw);
-      if (wait_warp(xw, n_pages & 1, 35)) {
+      pair_sync();
+      if (ok) {
         l += xl[(half ^ 1) * 128 + r];
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         __nv_bfloat16* dst = a.out + ((size_t)(tok0 + (R < rows_total ? R / G : 0)) * a.heads + kh * G + R % G) * HD + half * (HD / 2);
