@@ -54,6 +54,10 @@ class Stepper:
         self.meta = MetaStager(self.device, cache.n_groups, cache.stride)
         self._graphs: dict = {}
         self._seen_decode: set = set()
+        self._seen_chunk: set = set()
+        self._chunk_logits: torch.Tensor | None = None
+        self.max_graph_rows = 64        # steps of many tokens are recorded only if they want at most this many rows of logits
+        self.max_chunk_graphs = 16      # recordings of such steps kept at a time
         self._decode_logits: torch.Tensor | None = None
         self._graph_key = None
         self.check_kernels = os.environ.get("SLEUTH_B200_CHECK", "0") == "1"   # read the kernels' status word after each step
@@ -136,7 +140,9 @@ class Stepper:
         dest_a = np.asarray(dest, dtype=np.int64)[order] if dest else np.zeros(0, dtype=np.int64)
         b = self.meta.upload(c_slots, c_past, c_counts, tokens, rows_a, book.tables_for(c_slots))
         W = rows_a.shape[0]
-        if W and np.array_equal(dest_a, np.arange(dest_a[0], dest_a[0] + W)):
+        if self._chunk_by_graph(b, W, out, dest_a):
+            pass
+        elif W and np.array_equal(dest_a, np.arange(dest_a[0], dest_a[0] + W)):
             self.model.forward(b, self.cache, self.ws, out[int(dest_a[0]):int(dest_a[0]) + W])
         elif W:
             mark = self.ws.mark()
@@ -147,6 +153,51 @@ class Stepper:
         else:
             self.model.forward(b, self.cache, self.ws, out[:0])
         book.commit(c_slots, new_lens)
+
+    def _chunk_by_graph(self, b, W: int, out, dest_a) -> bool:
+        """A step of many tokens whose shape (tokens, sequences, longest share, wanted rows) has been seen before is
+        recorded once as a CUDA graph and replayed from then on: the host then no longer issues some two hundred
+        launches per step, which for short prompts is most of the step's time. Lengths, positions and tables live
+        in the device buffer that the upload refreshed, so one recording serves every step of that shape. The logits
+        land in a buffer of the stepper's and are copied to ``out``. Returns False if the step was not run."""
+        if not (self.use_graphs and getattr(self.model, "capturable", True) and 0 < W <= self.max_graph_rows):
+            return False
+        self._check_graph_key()
+        gkey = ("chunk", b.T, b.n, b.max_count, W)
+        graph = self._graphs.get(gkey)
+        if graph is None and gkey not in self._seen_chunk:
+            self._seen_chunk.add(gkey)
+            if len(self._seen_chunk) > 4096:
+                self._seen_chunk.clear()
+            return False
+        if self._chunk_logits is None or self._chunk_logits.shape[0] < W:
+            self._chunk_logits = torch.empty((max(W, 8), self.model.vocab), dtype=torch.float32, device=self.device)
+            for k in [k for k in self._graphs if isinstance(k[0], str)]:
+                del self._graphs[k]
+            graph = None
+        logits = self._chunk_logits[:W]
+        if graph is None:
+            if sum(1 for k in self._graphs if isinstance(k[0], str)) >= self.max_chunk_graphs:
+                for k in [k for k in self._graphs if isinstance(k[0], str)]:
+                    del self._graphs[k]
+            before = ops.lib().launches
+            graph = self._graphs[gkey] = self._capture(b, logits)
+            self._graph_own[gkey] = ops.lib().launches - before
+            ops.lib().launches = before          # captured, not run
+        graph.replay()
+        self.graph_kernel_launches += self._graph_own[gkey]
+        if np.array_equal(dest_a, np.arange(dest_a[0], dest_a[0] + W)):
+            out[int(dest_a[0]):int(dest_a[0]) + W].copy_(logits)
+        else:
+            out.index_copy_(0, torch.from_numpy(dest_a).to(self.device), logits)
+        return True
+
+    def _check_graph_key(self) -> None:
+        """Recordings hold addresses of the workspace and of the metadata buffer: when either was replaced, they go."""
+        key = (self.ws.generation, self.meta.generation)
+        if key != self._graph_key:
+            self._graphs.clear()
+            self._graph_key = key
 
     # ------------------------------------------------------------------ decode ----
     def _decode(self, entries, slots, toks, floats) -> torch.Tensor:
@@ -196,10 +247,7 @@ class Stepper:
             self._graphs.clear()
         logits = self._decode_logits[:n]
 
-        key = (self.ws.generation, self.meta.generation)
-        if key != self._graph_key:
-            self._graphs.clear()
-            self._graph_key = key
+        self._check_graph_key()
         gkey = (n, b.ids_map is not None)
         graph = self._graphs.get(gkey)
         if graph is not None:

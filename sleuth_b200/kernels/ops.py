@@ -36,9 +36,9 @@ def _need(cond: bool, msg: str) -> None:
 
 def _cuda(*tensors) -> None:
     for t in tensors:
-        if t is not None:
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
             _need(t.is_cuda, "the kernels of sleuth_b200 run on CUDA tensors only")
-            _need(t.is_contiguous(), f"tensor of shape {tuple(t.shape)} must be contiguous")
+            _need(False, f"tensor of shape {tuple(t.shape)} must be contiguous")
 
 
 def embed(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0, stream=None,
@@ -287,10 +287,14 @@ _TC_STATUS: dict = {}
 
 
 def _tc_status(device) -> torch.Tensor:
-    key = str(device)
-    if key not in _TC_STATUS:
-        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _TC_STATUS[key]
+    st = _TC_STATUS.get(device)
+    if st is None:
+        st = _TC_STATUS.get(str(device))
+        if st is None:
+            st = torch.zeros(1, dtype=torch.int32, device=device)
+            _TC_STATUS[str(device)] = st
+        _TC_STATUS[device] = st
+    return st
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None) -> None:

@@ -149,6 +149,7 @@ class Workspace:
         self.high = 0
         self.generation = 0
         self.frozen = False
+        self._views: dict = {}
 
     def mark(self) -> int:
         return self.top
@@ -156,11 +157,14 @@ class Workspace:
     def release(self, mark: int) -> None:
         self.top = mark
 
+    _ITEM = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8, torch.uint8: 1,
+             torch.int8: 1, torch.float64: 8, torch.int16: 2, torch.bool: 1}
+
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * self._ITEM[dtype]
         start = (self.top + self.ALIGN - 1) // self.ALIGN * self.ALIGN
         if start + nbytes > self.buf.numel():
             if self.frozen:
@@ -170,6 +174,16 @@ class Workspace:
             self.generation += 1
             self.top = 0
             start = 0
+            self._views.clear()
         self.top = start + nbytes
-        self.high = max(self.high, self.top)
-        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+        if self.top > self.high:
+            self.high = self.top
+        # the same requests come back step after step at the same places: the views are kept
+        key = (start, dtype, tuple(shape))
+        view = self._views.get(key)
+        if view is None:
+            if len(self._views) > 4096:
+                self._views.clear()
+            view = self.buf[start:start + nbytes].view(dtype).view(*shape)
+            self._views[key] = view
+        return view

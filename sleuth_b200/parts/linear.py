@@ -25,14 +25,16 @@ import os
 
 # Which kernel multiplies how many rows (bfloat16), as measured on a B200 with the Qwen3-0.6B shapes:
 #   up to SKINNY_ROWS rows   the weight-streaming kernel (equal to the library at 32 rows, behind it at 64)
-#   from TC_ROWS rows on     this package's tcgen05 kernel (level with the library at 2,048 rows, ahead with the
-#                            gated epilogue, behind it for a few hundred rows, where its 128-row tiles are few)
-#   between                  the library product (cuBLAS through torch.mm)
+#   from TC_ROWS rows on     this package's tcgen05 kernel (level with the library at 2,048 rows product by product,
+#                            ahead with its fused epilogues: a 128-token prompt takes 2.4 ms against 3.6 ms, a
+#                            1,024-token one 3.2 ms either way)
+#   between                  the library product (cuBLAS through torch.mm): fewer than 128 rows leave most of the
+#                            tcgen05 kernel's 128-row tiles empty
 # SLEUTH_B200_GEMM=own sends everything the own kernels take to them, =library everything above SKINNY_ROWS to cuBLAS.
 _CHOICE = os.environ.get("SLEUTH_B200_GEMM", "auto")
 USE_TC = _CHOICE != "library"
 SKINNY_ROWS = 64 if _CHOICE == "own" else 32
-TC_ROWS = 1 if _CHOICE == "own" else 1024
+TC_ROWS = 1 if _CHOICE == "own" else 128
 
 
 def use_skinny(M: int, N: int, K: int, norm: bool = False) -> bool:
