@@ -2,13 +2,13 @@
 
 * float32 run: the package's own FMA kernel (``csrc/gemm_f32.cu``); no tensor-core mode, and every
   output element sums over k in one fixed order whatever the number of rows.
-* bfloat16 run, up to 16 rows (decode steps): the package's weight-streaming tensor-core kernel
+* bfloat16 run, up to 32 rows (decode steps): the package's weight-streaming tensor-core kernel
   (``csrc/gemm_skinny.cu``), with the residual add or the float32 store in its epilogue.
-* bfloat16 run, more rows: the package's tcgen05/TMA kernel (``csrc/gemm_tc.cu``: operands by TMA into
-  swizzled shared memory, accumulation in tensor memory, the same epilogues). Only when the inner
-  dimension is no multiple of 8 (TMA needs 16-byte rows) does the product go to a library (cuBLAS through
-  ``torch.mm``, float32 accumulation), as the reference's ``nn.Linear`` always does
-  (sleuth/forge/model/attention.py:106-108).
+* bfloat16 run, 128 rows or more: the package's tcgen05/TMA kernel (``csrc/gemm_tc.cu``: operands by TMA into
+  swizzled shared memory, accumulation in tensor memory, the same epilogues).
+* bfloat16 run, between those, or an inner dimension that is no multiple of 8 (TMA needs 16-byte rows): a library
+  product (cuBLAS through ``torch.mm``, float32 accumulation), as the reference's ``nn.Linear`` always is
+  (sleuth/forge/model/attention.py:106-108). The thresholds and what they were measured on stand below.
 
 ``into`` adds the product to a float32 tensor (the residual stream) instead of returning it.
 """
