@@ -423,6 +423,16 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
+static int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
 template <int BN, bool QKV = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s, const TcQkv& qa = TcQkv{}) {
   constexpr int kStages = tc_stages(BN);
@@ -435,12 +445,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs&
   }
   const int cols_per_tile = a.mode == kTcSwiglu ? BN / 2 : BN;
   const long long total = (long long)((a.N + cols_per_tile - 1) / cols_per_tile) * ((a.M + kTcBM - 1) / kTcBM);
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
+  const int sms = sm_count();
   dim3 grid((unsigned)(total < sms ? total : sms));
   launch_prefetching(gemm_tc_kernel<BN, QKV>, grid, dim3(QKV ? kTcThreads + 128 : kTcThreads), (size_t)smem, s, mx, mw, a, qa);
   return check_launch("gemm_tc");
@@ -462,11 +467,17 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0),
               "gemm_tc: X, W and C must be 16-byte aligned");
   const bool gated = mode == kTcSwiglu;
-  // The widest tile that still gives the GPU about a hundred tiles to work on: wide tiles reuse the X tile for more
-  // columns, narrow ones keep every SM streaming weights when there are few rows.
+  // Tile width: the narrowest tile with which all tiles still run at once (one per SM). Measured with 1,024 columns:
+  // within one round a narrower tile is a little faster (more SMs stream operands), while a second round costs
+  // nearly twice (768 rows: 17 us with 96 tiles of 64 columns, 28 us with 192 of 32). When even the widest tile
+  // needs several rounds, the widest is the most efficient.
   const long long m_tiles = (M + 127) / 128;
+  const int sms = sm_count();
   int bn = 256;
-  while (bn > (gated ? 64 : 32) && m_tiles * ((N + (gated ? bn / 2 : bn) - 1) / (gated ? bn / 2 : bn)) < 100) bn >>= 1;
+  for (int cand = gated ? 64 : 32; cand <= 256; cand <<= 1) {
+    const int cols = gated ? cand / 2 : cand;
+    if (m_tiles * ((N + cols - 1) / cols) <= sms) { bn = cand; break; }
+  }
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, kTcBM);
   if (rc) return rc;
