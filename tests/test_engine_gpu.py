@@ -157,6 +157,37 @@ def test_chunked_prompt_and_wanted_rows_in_any_order(dtype, model_folders):
     torch.testing.assert_close(out, want_rows, **TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_steps_of_a_repeated_shape_are_recorded_and_still_right(dtype, model_folders):
+    """The second step of a shape (tokens, sequences, longest share, wanted rows) is recorded as a CUDA graph and
+    replayed from then on. Different tokens, different slots, a different past (a later chunk of a longer prompt)
+    and a different split of the same number of tokens between two sequences must each give the plain result."""
+    eng, ref = load(model_folders["D"], dtype), oracle(model_folders["D"], dtype)
+    reqs = requests_for("D", [150, 150, 150, 300, 150], seed=9)
+    seen = 0
+    for i, ids in enumerate(reqs[:3]):                     # same shape three times: eager, recorded, replayed
+        (slot,) = eng.open(1)
+        got = eng.step([(slot, ids, (0, 149))]).cpu()
+        torch.testing.assert_close(got, ref(ids)[[0, 149]], **TOL[dtype])
+        if i == 0:
+            held = slot                                     # keep one slot busy so that later ones differ
+        else:
+            eng.close([slot])
+        seen = max(seen, sum(1 for k in eng.stepper._graphs if isinstance(k[0], str)))
+    assert seen == 1
+    (slot,) = eng.open(1)                                   # the same shape as the second chunk of a longer prompt
+    eng.step([(slot, reqs[3][:150], ())])
+    got = eng.step([(slot, reqs[3][150:], (0, 149))]).cpu()
+    torch.testing.assert_close(got, ref(reqs[3])[[150, 299]], **TOL[dtype])
+    eng.close([slot, held])
+    a, b = requests_for("D", [100, 50], seed=10), requests_for("D", [70, 80], seed=11)
+    for pair in (a, b, b[::-1]):                            # 150 tokens in two sequences: shapes (100, ...) and (80, ...)
+        slots = eng.open(2)
+        got = eng.step([(slots[0], pair[0], (len(pair[0]) - 1,)), (slots[1], pair[1], (len(pair[1]) - 1,))]).cpu()
+        torch.testing.assert_close(got, torch.stack([ref(pair[0])[-1], ref(pair[1])[-1]]), **TOL[dtype])
+        eng.close(slots)
+
+
 def test_float32_is_bitwise_schedule_independent(model_folders):
     """In float32 every kernel sums in an order that depends on the token's own position only, so a request
     gives the same bits alone, token by token and inside a batch."""
