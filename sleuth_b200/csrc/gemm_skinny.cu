@@ -53,15 +53,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 constexpr int kSkinnyWarps = 8;
+constexpr int kNormPad = 64;          // bytes between the normalised rows in shared memory, against bank conflicts
+constexpr int kNormMaxK = 4096;      // widest stream the fused norm takes (16 rows of it must fit shared memory)
 // Blocks of 32 k values whose weights a warp fetches before it uses any: 8 sixteen-byte loads per lane in flight.
 __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 : (tiles >= 4 ? 2 : (tiles >= 2 ? 4 : 8)); }
 
 // NORM: X is not given; instead the block reads the float32 stream and applies the RMSNorm itself,
-// y = rmsnorm(x) W^T with rmsnorm(x) = x * gain / sqrt(mean(x^2) + eps) (sleuth/forge/model/norm.py:50). The row
-// factor 1/sqrt(..) is a scalar per row, so it is taken out of the product: the tensor cores multiply
-// bfloat16(x * gain) and the factor is applied to the float32 sums in the epilogue. The sum of squares is
-// gathered from the same loads that feed the product, so the norm costs no extra pass, no extra kernel and no
-// wait in front of the product.
+// rmsnorm(x) = (x / sqrt(mean(x^2) + eps)) * gain (sleuth/forge/model/norm.py:50): after the wait for the kernel in
+// front, each of the eight warps takes a row (two, above eight rows), sums its squares, and writes the normalised
+// row as bfloat16 into shared memory, from where all warps then take their token fragments. The weights of the
+// first batch are already on their way at that time, so the norm costs no kernel of its own and hides behind
+// the weight stream. Every block normalises all rows again (they come from L2): 16 rows of 1,024 are 64 KB.
 // Two blocks per SM are asked for where a warp multiplies a single tile of weight rows (the narrow matrices, whose
 // blocks are many and short): measured faster there, slower for the two-tile shapes. Three for the four-tile shape
 // that serves very wide matrices (the output matrix over the vocabulary): 80 registers, no spills, 4.9 instead of
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   constexpr int kUnroll = unroll_for(TILES);
   static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
   __shared__ float red[kSkinnyWarps][TILES][16 * MT][8 + 1];
-  __shared__ float ssq_part[kSkinnyWarps][16];
+  extern __shared__ __align__(16) unsigned char normed_rows[];      // NORM: [16][K * 2 + kNormPad] bytes
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NF * 8);
@@ -93,8 +95,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   }
   const __nv_bfloat16* xrow0 = (!NORM && g < a.M) ? a.X + (size_t)g * a.K + 8 * t : nullptr;
   const __nv_bfloat16* xrow1 = (!NORM && g + 8 < a.M) ? a.X + (size_t)(g + 8) * a.K + 8 * t : nullptr;
-  const float* frow0 = (NORM && g < a.M) ? a.Xf + (size_t)g * a.K + 8 * t : nullptr;
-  const float* frow1 = (NORM && g + 8 < a.M) ? a.Xf + (size_t)(g + 8) * a.K + 8 * t : nullptr;
+  const int norm_stride = a.K * 2 + kNormPad;
 
   float acc[MT][TILES][4];
 #pragma unroll
@@ -131,7 +132,30 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
                        ? reinterpret_cast<const float*>(a.C)[(size_t)r * a.ldc + feat] : 0.0f;
     }
   }
-  float ssq0 = 0.0f, ssq1 = 0.0f;     // NORM: sums of squares of this lane's share of rows g and g + 8
+  if (NORM) {
+    for (int r = warp; r < 16; r += kSkinnyWarps) {
+      uint2* dst = reinterpret_cast<uint2*>(normed_rows + (size_t)r * norm_stride);
+      if (r >= a.M) {        // rows that do not exist multiply as zeros
+        for (int c = lane; c < a.K / 4; c += 32) dst[c] = make_uint2(0u, 0u);
+        continue;
+      }
+      const float4* src = reinterpret_cast<const float4*>(a.Xf + (size_t)r * a.K);
+      float ss = 0.0f;
+      for (int c = lane; c < a.K / 4; c += 32) {
+        const float4 v = src[c];
+        ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+      const float4* gn = reinterpret_cast<const float4*>(a.gain);
+      for (int c = lane; c < a.K / 4; c += 32) {
+        const float4 v = src[c], gv = gn[c];
+        dst[c] = make_uint2(pack2((v.x * inv) * gv.x, (v.y * inv) * gv.y), pack2((v.z * inv) * gv.z, (v.w * inv) * gv.w));
+      }
+    }
+    __syncthreads();
+  }
   for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
     if (kb != kb_begin) fetch_weights(kb);
     if (MT > 1) {
@@ -159,28 +183,9 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
       const bool live = kb + u < kb_end;
       const int off = (kb + u) * 32;
       if (NORM) {
-        x0[u] = zero;
-        x1[u] = zero;
-        if (live) {
-          const float4 g0 = *reinterpret_cast<const float4*>(a.gain + off + 8 * t);
-          const float4 g1 = *reinterpret_cast<const float4*>(a.gain + off + 8 * t + 4);
-          if (frow0) {
-            const float4 p = *reinterpret_cast<const float4*>(frow0 + off), q = *reinterpret_cast<const float4*>(frow0 + off + 4);
-            ssq0 += (p.x * p.x + p.y * p.y) + (p.z * p.z + p.w * p.w) + (q.x * q.x + q.y * q.y) + (q.z * q.z + q.w * q.w);
-            x0[u].x = pack2(p.x * g0.x, p.y * g0.y);
-            x0[u].y = pack2(p.z * g0.z, p.w * g0.w);
-            x0[u].z = pack2(q.x * g1.x, q.y * g1.y);
-            x0[u].w = pack2(q.z * g1.z, q.w * g1.w);
-          }
-          if (frow1) {
-            const float4 p = *reinterpret_cast<const float4*>(frow1 + off), q = *reinterpret_cast<const float4*>(frow1 + off + 4);
-            ssq1 += (p.x * p.x + p.y * p.y) + (p.z * p.z + p.w * p.w) + (q.x * q.x + q.y * q.y) + (q.z * q.z + q.w * q.w);
-            x1[u].x = pack2(p.x * g0.x, p.y * g0.y);
-            x1[u].y = pack2(p.z * g0.z, p.w * g0.w);
-            x1[u].z = pack2(q.x * g1.x, q.y * g1.y);
-            x1[u].w = pack2(q.z * g1.z, q.w * g1.w);
-          }
-        }
+        const unsigned char* base = normed_rows + (size_t)(off + 8 * t) * 2;
+        x0[u] = live ? *reinterpret_cast<const uint4*>(base + (size_t)g * norm_stride) : zero;
+        x1[u] = live ? *reinterpret_cast<const uint4*>(base + (size_t)(g + 8) * norm_stride) : zero;
       } else {
         x0[u] = (live && xrow0) ? *reinterpret_cast<const uint4*>(xrow0 + off) : zero;
         x1[u] = (live && xrow1) ? *reinterpret_cast<const uint4*>(xrow1 + off) : zero;
@@ -206,15 +211,6 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
       red[warp][f][16 * mt + g + 8][2 * t] = acc[mt][f][2];
       red[warp][f][16 * mt + g + 8][2 * t + 1] = acc[mt][f][3];
     }
-  if (NORM) {
-    // the eight warps' slices of K cover every element of rows 0..15 exactly once, so the row sums of squares
-    // come from the very loads that fed the product: lanes of a quad, then warps, added in a fixed order
-    ssq0 += __shfl_xor_sync(0xffffffffu, ssq0, 1);
-    ssq0 += __shfl_xor_sync(0xffffffffu, ssq0, 2);
-    ssq1 += __shfl_xor_sync(0xffffffffu, ssq1, 1);
-    ssq1 += __shfl_xor_sync(0xffffffffu, ssq1, 2);
-    if (t == 0) { ssq_part[warp][g] = ssq0; ssq_part[warp][g + 8] = ssq1; }
-  }
   __syncthreads();
 
 #pragma unroll
@@ -228,19 +224,10 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
     float v = 0.0f;
 #pragma unroll
     for (int w8 = 0; w8 < kSkinnyWarps; ++w8) v += red[w8][f][r][cc];
-    float inv = 1.0f;
-    if (NORM) {
-      float ss = 0.0f;
-#pragma unroll
-      for (int w8 = 0; w8 < kSkinnyWarps; ++w8) ss += ssq_part[w8][r];
-      inv = 1.0f / sqrtf(ss / (float)a.K + a.eps);
-      v *= inv;
-    }
     if (MODE == kSwiglu) {
       float u = 0.0f;
 #pragma unroll
       for (int w8 = 0; w8 < kSkinnyWarps; ++w8) u += red[w8][NF + f][r][cc];
-      u *= inv;
       v = (v / (1.0f + expf(-v))) * u;
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
     } else if (MODE == kStoreBf16) {
@@ -253,23 +240,36 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   }
 }
 
+template <int NF, int MODE, bool NORM, int MT>
+static int launch_skinny_mode(const SkinnyArgs& a, cudaStream_t s) {
+  const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
+  const size_t smem = NORM ? (size_t)16 * (a.K * 2 + kNormPad) : 0;
+  if (NORM) {
+    static bool configured = false;
+    if (!configured) {
+      const int most = 16 * (kNormMaxK * 2 + kNormPad);
+      cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NF, MODE, NORM, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+      if (e != cudaSuccess) return fail(2, "gemm_skinny: cannot reserve %d bytes of shared memory: %s", most, cudaGetErrorString(e));
+      configured = true;
+    }
+  }
+  launch_prefetching(gemm_skinny_kernel<NF, MODE, NORM, MT>, dim3(blocks), dim3(kSkinnyWarps * 32), smem, s, a);
+  return check_launch("gemm_skinny");
+}
+
 template <int NF, bool NORM, int MT>
 static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
-  const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
-  const int threads = kSkinnyWarps * 32;
   switch (mode) {
-    case kStoreBf16: launch_prefetching(gemm_skinny_kernel<NF, kStoreBf16, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kStoreF32: launch_prefetching(gemm_skinny_kernel<NF, kStoreF32, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
-    case kAddF32: launch_prefetching(gemm_skinny_kernel<NF, kAddF32, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a); break;
+    case kStoreBf16: return launch_skinny_mode<NF, kStoreBf16, NORM, MT>(a, s);
+    case kStoreF32: return launch_skinny_mode<NF, kStoreF32, NORM, MT>(a, s);
+    case kAddF32: return launch_skinny_mode<NF, kAddF32, NORM, MT>(a, s);
     default:
       if constexpr (2 * NF * MT <= 8) {      // gate and up tiles of every row tile must fit the partial-sum buffer
-        launch_prefetching(gemm_skinny_kernel<NF, kSwiglu, NORM, MT>, dim3(blocks), dim3(threads), 0, s, a);
+        return launch_skinny_mode<NF, kSwiglu, NORM, MT>(a, s);
       } else {
         return fail(1, "gemm_skinny: the gated epilogue is not built for %d features a block with %d rows", NF * 8, 16 * MT);
       }
-      break;
   }
-  return check_launch("gemm_skinny");
 }
 
 template <bool NORM>
@@ -314,8 +314,9 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
 // `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
 extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
                                     int K, int ldc, int mode, void* stream) {
-  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16,
-              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32)", M, N, K);
+  SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16 && K <= kNormMaxK,
+              "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32, at most %d)",
+              M, N, K, kNormMaxK);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N && eps > 0.0f, "gemm_skinny: mode=%d ldc=%d N=%d eps=%g", mode, ldc, N, (double)eps);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)gain % 16 == 0),
               "gemm_skinny: X, gain and W must be 16-byte aligned");

@@ -247,8 +247,9 @@ SKINNY_MODES = {"bf16": 0, "f32": 1, "add": 2, "swiglu": 3}
 
 
 def skinny_supported(M: int, N: int, K: int, norm: bool = False) -> bool:
-    """Whether the few-rows bfloat16 product kernel takes this problem (with the norm fused in: up to 16 rows)."""
-    return 1 <= M <= (16 if norm else 64) and K >= 32 and K % 32 == 0 and N >= 1
+    """Whether the few-rows bfloat16 product kernel takes this problem (with the norm fused in: up to 16 rows of
+    at most 4,096 values, which it keeps normalised in shared memory)."""
+    return 1 <= M <= (16 if norm else 64) and K >= 32 and K % 32 == 0 and N >= 1 and (not norm or K <= 4096)
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None) -> None:

@@ -376,7 +376,8 @@ def test_argmax_first_index_on_ties(rows, vocab, limit):
 @pytest.mark.parametrize("M,N,K,mode", [(1, 4096, 1024, "bf16"), (8, 1024, 2048, "f32"), (16, 200, 96, "bf16"),
                                          (5, 3072, 1024, "swiglu"), (3, 136, 64, "swiglu")])
 def test_gemm_skinny_with_the_norm_fused_in(M, N, K, mode):
-    """The product that normalises its input rows itself equals norm then product, up to where h is rounded."""
+    """The product that normalises its input rows itself equals norm then product: the rows are normalised in
+    float32 and rounded to bfloat16 once, as the norm kernel does."""
     o = ops()
     g = torch.Generator().manual_seed(N + K)
     x = torch.randn(M, K, generator=g) * 2
@@ -384,9 +385,8 @@ def test_gemm_skinny_with_the_norm_fused_in(M, N, K, mode):
     eps = 1e-5
     rows = 2 * N if mode == "swiglu" else N
     w = (torch.randn(rows, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
-    # the kernel multiplies bfloat16(x * gain) and applies the row factor 1/sqrt(mean(x^2) + eps) to the sums
-    inv = torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
-    hb = (x * gain).to(torch.bfloat16).double() * inv
+    inv = torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float()
+    hb = ((x * inv) * gain).to(torch.bfloat16).double()
     if mode == "swiglu":
         a, b = hb @ w[:N].double().T, hb @ w[N:].double().T
         ref = a * torch.sigmoid(a) * b
