@@ -43,11 +43,12 @@ def requests_for(name, lengths, seed=0):
     return [rng.integers(0, tiny.CONFIGS[name]["vocab_size"], size=n).tolist() for n in lengths]
 
 
-LENGTHS = {"A": [5, 11, 17, 70], "B": [1, 7, 23, 40, 130], "C": [3, 64, 65, 150, 33], "D": [40, 1, 200, 129]}
+LENGTHS = {"A": [5, 11, 17, 70], "B": [1, 7, 23, 40, 130], "C": [3, 64, 65, 150, 33], "D": [40, 1, 200, 129],
+           "E": [10, 140, 300, 129]}
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_each_request_alone_and_whole(name, dtype, model_folders):
     eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
     for ids in requests_for(name, LENGTHS[name]):
@@ -58,7 +59,7 @@ def test_each_request_alone_and_whole(name, dtype, model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_32_tokens_one_by_one(name, dtype, model_folders):
     eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
     for ids in requests_for(name, [n for n in LENGTHS[name] if n > 32] + [33]):
@@ -72,7 +73,7 @@ def test_last_32_tokens_one_by_one(name, dtype, model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_one_after_another_reuse_slots(name, dtype, model_folders):
     """Three batches through a cache with room for one batch only. Within a batch the requests have unequal
     prompts and unequal numbers of decoded tokens, so the shorter ones end earlier; the next batch gets

@@ -27,5 +27,13 @@ D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=640,
          rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False, tie_word_embeddings=False,
          max_position_embeddings=1024)
 
-CONFIGS = {"A": A, "B": B, "C": C, "D": D}
-SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44}
+# head_dim 64 with a group of 4 (a divisor of 128): prompts of this one run the tensor-memory attention kernel and
+# the q/k/v product with its fused epilogue at head size 64, with biases, and with a window on the middle layer
+E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777, hidden_size=192,
+         intermediate_size=264, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+         rope_theta=100000.0, rms_norm_eps=2e-6, attention_bias=True, tie_word_embeddings=False,
+         max_position_embeddings=512, sliding_window=48,
+         layer_types=["full_attention", "sliding_attention", "full_attention"])
+
+CONFIGS = {"A": A, "B": B, "C": C, "D": D, "E": E}
+SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44, "E": 55}
