@@ -67,12 +67,14 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // Two blocks per SM are asked for where a warp multiplies a single tile of weight rows (the narrow matrices, whose
 // blocks are many and short): measured faster there, slower for the two-tile shapes. Three for the four-tile shape
 // that serves very wide matrices (the output matrix over the vocabulary): 80 registers, no spills, 4.9 instead of
-// 4.6 TB/s; four would spill.
+// 4.6 TB/s; four would spill. Three also for the gated shape with one tile pair per warp: the gate/up product of a
+// single-token step has 384 blocks, which then run at once on 148 SMs instead of in two rounds (1.150 -> 1.098 ms a
+// step at batch 8).
 // MT: token rows come in tiles of 16; MT = 1 serves up to 16 rows, MT = 2 up to 32, MT = 4 up to 64. With MT > 1
 // the token fragments are fetched as they are needed (they sit in L1 after the first block of an SM has read them)
 // while the weight loads still go out in one batch.
 template <int NF, int MODE, bool NORM, int MT>
-__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : ((NF == 4 && MT == 1 && !NORM) ? 3 : 1)) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : (((NF == 4 && MT == 1 && !NORM) || (MODE == kSwiglu && NF == 1 && MT == 1 && !NORM)) ? 3 : 1)) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   constexpr int kUnroll = unroll_for(TILES);
   static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
