@@ -43,6 +43,21 @@ def test_rmsnorm(dim, dtype):
     torch.testing.assert_close(out2.cpu().double(), ref[[5, 0, 3]], **tol(dtype))
 
 
+@pytest.mark.parametrize("dim", [1024, 1000, 2048, 4100])
+def test_rmsnorm_many_rows(dim):
+    """Prompts bring a thousand rows and more; the bfloat16 run then takes another block shape."""
+    g = torch.Generator().manual_seed(dim + 1)
+    n = 1100
+    x = torch.randn(n, dim, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(dim, generator=g)
+    eps = 1e-6
+    ref = (x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * w.double())
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((n, dim), float("nan"), dtype=dtype, device=DEV)
+        ops().rmsnorm(x.to(DEV), w.to(DEV), out, eps)
+        torch.testing.assert_close(out.cpu().double(), ref, **tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embed_add_swiglu(dtype):
     g = torch.Generator().manual_seed(0)
