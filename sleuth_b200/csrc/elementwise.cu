@@ -168,7 +168,7 @@ extern "C" int slb_rmsnorm(const float* x, const float* w, void* out, int out_dt
     // Many rows (prompts), bfloat16 run: half the threads per row, so that twice as many rows are resident and a
     // 2,048-row call runs in one round of blocks instead of two. The float32 run keeps one block shape whatever
     // the row count, so that a row's sum is formed in the same order in every step.
-    if (out_dtype == kBF16 && n_rows >= 1024 && threads == 256) threads = 128;
+    if (out_dtype == kBF16 && n_rows >= 1024 && threads == 256 && n4 <= 8 * 128) threads = 128;
     const int per = (n4 + threads - 1) / threads;      // at most 8
     #define SLB_NORM(P)                                                                                              \
       if (out_dtype == kF32) launch(rmsnorm_vec_kernel<float, P>, dim3(n_rows), dim3(threads), 0, s, x, w, (float*)out, rows, dim, eps); \
