@@ -74,7 +74,7 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // the token fragments are fetched as they are needed (they sit in L1 after the first block of an SM has read them)
 // while the weight loads still go out in one batch.
 template <int NF, int MODE, bool NORM, int MT>
-__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : (((NF == 4 && MT == 1 && !NORM) || (MODE == kSwiglu && NF == 1 && MT == 1 && !NORM)) ? 3 : 1)) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : (((NF == 4 && MT == 1 && !NORM) || (MODE == kSwiglu && NF == 1 && MT <= 2 && !NORM)) ? 3 : 1)) gemm_skinny_kernel(SkinnyArgs a) {
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   constexpr int kUnroll = unroll_for(TILES);
   static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
