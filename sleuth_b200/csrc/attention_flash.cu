@@ -294,7 +294,6 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
 // grid: (splits * row_tiles, kv_heads, sequences); every sequence has count 1.
 // Three page buffers: while one page is being multiplied, the next two are already on their way, which is what
 // keeps the memory system busy when a block's work per page is short compared with the latency of a load.
-constexpr int kDecodeStages = 3;
 
 // One row of the raw q/k/v projection, as csrc/qkv_post.cu treats it: + bias, RMSNorm over the head with `gain`
 // (when given), rotation of the whole head by the token's angles (when tables are given); float32 throughout.
@@ -344,7 +343,10 @@ __device__ __forceinline__ void put_row(unsigned char* tile, int row, int lane, 
   }
 }
 
-template <int HD>
+// S: page buffers per block. Three (two pages on their way while one is worked on) is the default; with two, three
+// blocks fit an SM instead of two, which lets two slices per (sequence, kv head) run at once where one slice each
+// would leave half the GPU idle (see decode_stages).
+template <int HD, int S>
 __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
   // Fused form: the keys and values of earlier tokens, the block table and the lengths were all written before the
   // kernel that precedes this one began, so pages are requested before the wait for that kernel (which produces
@@ -354,7 +356,6 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   if (!fused) pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;
-  constexpr int S = kDecodeStages;
   constexpr int EPL = HD / 32;
   const uint32_t sK = smem_u32(smem), sV = sK + S * TILE;
   const uint32_t sQ = sV + S * TILE;          // [16][HD]
@@ -397,8 +398,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     cp_async_commit();
   };
   if (my_lo <= my_hi) {
-    fetch(my_lo);
-    fetch(my_lo + 1);
+#pragma unroll
+    for (int d = 0; d < S - 1; ++d) fetch(my_lo + d);
   }
   // Nothing but read-only loads may come before this wait: the workspace this kernel writes to is shared with
   // kernels that may still be running.
@@ -453,8 +454,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
 
     for (int page = my_lo; page <= my_hi; ++page) {
       const int stage = (page - my_lo) % S;
-      fetch(page + 2);       // into the buffer that the page before this one has left
-      cp_async_wait<2>();    // all but the two newest groups: this page has landed
+      fetch(page + S - 1);       // into the buffer that the page before this one has left
+      cp_async_wait<S - 1>();    // all but the newest groups: this page has landed
       __syncthreads();
       if (owns_last && page == page_hi) {     // put the new token's key and value where the cache copy has a stale row
         if (warp < 2) put_row<HD>(smem + ((warp == 0 ? 0 : S) + stage) * TILE, pos % 64, lane, new_kv);
@@ -643,25 +644,41 @@ static int launch_prefill(const FlashArgs& a, int n_seqs, int max_count, cudaStr
   return check_launch("attention (prefill)");
 }
 
-template <int HD>
-static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
+// Two page buffers instead of three when that makes all blocks resident at once: with three buffers two blocks fit
+// an SM (296 in all), with two buffers three (444).
+static int decode_stages(long long blocks) {
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  return (blocks > 2ll * sms && blocks <= 3ll * sms) ? 2 : 3;
+}
+
+template <int HD, int S>
+static int launch_decode_staged(const FlashArgs& a, int n_seqs, cudaStream_t s) {
   const int G = a.heads / a.kv_heads;
   const int row_tiles = (G + 15) / 16;
-  const int tiles_bytes = 2 * kDecodeStages * 64 * HD * 2 + 16 * HD * 2;
+  const int tiles_bytes = 2 * S * 64 * HD * 2 + 16 * HD * 2;
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * 4;
   const int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(2, "attention (decode): cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid(a.splits * row_tiles, a.kv_heads, n_seqs);
   if (a.qkv != nullptr)      // the fused form asks for its pages before it waits for the kernel in front of it
-    launch_prefetching(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
+    launch_prefetching(attn_decode_kernel<HD, S>, dim3(grid), dim3(kFlashThreads), smem, s, a);
   else
-    launch(attn_decode_kernel<HD>, dim3(grid), dim3(kFlashThreads), smem, s, a);
+    launch(attn_decode_kernel<HD, S>, dim3(grid), dim3(kFlashThreads), smem, s, a);
   return check_launch("attention (decode)");
+}
+
+template <int HD>
+static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
+  const int row_tiles = (a.heads / a.kv_heads + 15) / 16;
+  const long long blocks = (long long)a.splits * row_tiles * a.kv_heads * n_seqs;
+  return decode_stages(blocks) == 2 ? launch_decode_staged<HD, 2>(a, n_seqs, s) : launch_decode_staged<HD, 3>(a, n_seqs, s);
 }
 
 }  // namespace slb

@@ -131,11 +131,14 @@ def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> 
     GPU a few times over, never more than a sequence can have pages. It depends on the batch size
     only, not on the lengths, so a captured step stays valid as sequences grow."""
     blocks = max(1, n_seqs * kv_heads * ((group + 15) // 16))
-    # two blocks of this kernel fit an SM (100 KB of shared memory each at head size 128): 148 * 2 run at once.
+    # Two blocks of this kernel fit an SM with its three page buffers (100 KB of shared memory at head size 128),
+    # three with two buffers, which the launcher picks when that makes all blocks run at once: 148 * 2 or 148 * 3.
     # All slices should run in one wave.
     resident = 148 * 2
     if blocks >= resident:
         return 1
+    if 2 * blocks > resident and 2 * blocks <= 148 * 3 and table_stride >= 8:
+        return 2          # one slice each would leave half the GPU idle; two fit with two page buffers
     # merging the slices costs a few microseconds that grow with their number: a slice should hold at least
     # four pages of the longest sequence
     return max(1, min(resident // blocks, 64, max(1, table_stride // 4)))

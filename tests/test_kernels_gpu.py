@@ -236,6 +236,16 @@ def test_attention_decode_tensor_cores(splits, heads, kv_heads, hd):
     run_attention(splits, bf, heads, kv_heads, hd, pasts=[10, 200, 700], counts=[1] * 3, window=100, seed=6)
 
 
+def test_attention_decode_with_two_page_buffers():
+    """Between two and three blocks per SM the launcher takes the form with two page buffers (three blocks fit an SM
+    then): twenty sequences of eight kv heads in two slices are 320 blocks."""
+    bf = torch.bfloat16
+    pasts = [0, 63, 64, 300, 1000, 129, 700, 5, 450, 999] * 2
+    run_attention(2, bf, 16, 8, 128, pasts=pasts, counts=[1] * 20, window=0, seed=12)
+    run_attention(2, bf, 16, 8, 128, pasts=pasts, counts=[1] * 20, window=200, seed=13)
+    run_attention(1, bf, 8, 8, 64, pasts=pasts * 2, counts=[1] * 40, window=0, seed=14)       # 320 blocks of one slice
+
+
 def test_attention_far_key_decides():
     """One key far back gets a score that dominates: a kernel that drops or misplaces it fails loudly."""
     o = ops()
