@@ -54,7 +54,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 constexpr int kSkinnyWarps = 8;
 constexpr int kNormPad = 64;          // bytes between the normalised rows in shared memory, against bank conflicts
-constexpr int kNormMaxK = 4096;      // widest stream the fused norm takes (16 rows of it must fit shared memory)
+constexpr int kNormMaxK = 4096;      // widest stream the fused norm takes (16 rows of it fit shared memory)
 // Blocks of 32 k values whose weights a warp fetches before it uses any: 8 sixteen-byte loads per lane in flight.
 __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 : (tiles >= 4 ? 2 : (tiles >= 2 ? 4 : 8)); }
 
@@ -64,6 +64,7 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // row as bfloat16 into shared memory, from where all warps then take their token fragments. The weights of the
 // first batch are already on their way at that time, so the norm costs no kernel of its own and hides behind
 // the weight stream. Every block normalises all rows again (they come from L2): 16 rows of 1,024 are 64 KB.
+// Shared memory holds the rows that exist, so that a single wide row does not cost the SM its other blocks.
 // Two blocks per SM are asked for where a warp multiplies a single tile of weight rows (the narrow matrices, whose
 // blocks are many and short): measured faster there, slower for the two-tile shapes. Three for the four-tile shape
 // that serves very wide matrices (the output matrix over the vocabulary): 80 registers, no spills, 4.9 instead of
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   constexpr int kUnroll = unroll_for(TILES);
   static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
   __shared__ float red[kSkinnyWarps][TILES][16 * MT][8 + 1];
-  extern __shared__ __align__(16) unsigned char normed_rows[];      // NORM: [16][K * 2 + kNormPad] bytes
+  extern __shared__ __align__(16) unsigned char normed_rows[];      // NORM: [M][K * 2 + kNormPad] bytes
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NF * 8);
@@ -135,12 +136,8 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
     }
   }
   if (NORM) {
-    for (int r = warp; r < 16; r += kSkinnyWarps) {
+    for (int r = warp; r < a.M; r += kSkinnyWarps) {
       uint2* dst = reinterpret_cast<uint2*>(normed_rows + (size_t)r * norm_stride);
-      if (r >= a.M) {        // rows that do not exist multiply as zeros
-        for (int c = lane; c < a.K / 4; c += 32) dst[c] = make_uint2(0u, 0u);
-        continue;
-      }
       const float4* src = reinterpret_cast<const float4*>(a.Xf + (size_t)r * a.K);
       float ss = 0.0f;
       for (int c = lane; c < a.K / 4; c += 32) {
@@ -186,8 +183,8 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
       const int off = (kb + u) * 32;
       if (NORM) {
         const unsigned char* base = normed_rows + (size_t)(off + 8 * t) * 2;
-        x0[u] = live ? *reinterpret_cast<const uint4*>(base + (size_t)g * norm_stride) : zero;
-        x1[u] = live ? *reinterpret_cast<const uint4*>(base + (size_t)(g + 8) * norm_stride) : zero;
+        x0[u] = (live && g < a.M) ? *reinterpret_cast<const uint4*>(base + (size_t)g * norm_stride) : zero;
+        x1[u] = (live && g + 8 < a.M) ? *reinterpret_cast<const uint4*>(base + (size_t)(g + 8) * norm_stride) : zero;
       } else {
         x0[u] = (live && xrow0) ? *reinterpret_cast<const uint4*>(xrow0 + off) : zero;
         x1[u] = (live && xrow1) ? *reinterpret_cast<const uint4*>(xrow1 + off) : zero;
@@ -245,7 +242,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
 template <int NF, int MODE, bool NORM, int MT>
 static int launch_skinny_mode(const SkinnyArgs& a, cudaStream_t s) {
   const int blocks = (a.N + NF * 8 - 1) / (NF * 8);
-  const size_t smem = NORM ? (size_t)16 * (a.K * 2 + kNormPad) : 0;
+  const size_t smem = NORM ? (size_t)a.M * (a.K * 2 + kNormPad) : 0;     // rows that do not exist multiply as zeros
   if (NORM) {
     static bool configured = false;
     if (!configured) {

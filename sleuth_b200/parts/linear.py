@@ -37,7 +37,19 @@ SKINNY_ROWS = 64 if _CHOICE == "own" else 32
 TC_ROWS = 1 if _CHOICE == "own" else 128
 
 
+# The norm fused into the weight-streaming kernel pays as long as normalising all rows again in every block is short
+# beside the block's weight stream: measured against the norm kernel plus the plain product (us, q/k/v shapes):
+#   K 1,024: 1 row 3.5 / 4.1, 8 rows 4.2 / 5.0, 16 rows 5.7 / 5.3    K 2,048: 1 row 6.4 / 6.8, 8 rows 7.3 / 7.1
+#   K 2,560: 1 row 12.7 / 11.7, 8 rows 14.6 / 12.5                    K 4,096: 1 row 18.7 / 15.1, 8 rows 22.1 / 16.7
+# Inside a step the fused form saves a kernel boundary on top of that: at K 2,048 with 8 rows the step is 4 % faster
+# with it (1.660 against 1.726 ms), at K 4,096 6 % slower (1.626 against 1.528 ms with one row).
+NORM_FUSE_MAX_K = 2048
+NORM_FUSE_MAX_ELEMENTS = 16384
+
+
 def use_skinny(M: int, N: int, K: int, norm: bool = False) -> bool:
+    if norm and (K > NORM_FUSE_MAX_K or M * K > NORM_FUSE_MAX_ELEMENTS):
+        return False
     return M <= SKINNY_ROWS and ops.skinny_supported(M, N, K, norm)
 
 
