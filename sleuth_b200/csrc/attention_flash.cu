@@ -39,6 +39,7 @@ struct FlashArgs {
   int heads, kv_heads, window;
   float scale_log2;             // scale * log2(e)
   // decode only
+  NextRead next;                // what the kernel after this one reads (its weights), or nothing
   int splits;
   float* part_o;                // [n, H, splits, HD] unnormalised
   float* part_ml;               // [n, H, splits, 2]  running max (log2 units) and sum
@@ -536,6 +537,9 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     }
     cp_async_wait<0>();
   }
+  // this block has asked for its last page: the next kernel's weights may now use the memory system
+  if (tid == 0)
+    prefetch_share(a.next, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), gridDim.x * gridDim.y * gridDim.z);
 
   // merge the four warps (each saw different keys) through shared memory
 #pragma unroll
@@ -719,7 +723,8 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
                                     int splits, float* scratch, long long scratch_floats, int* counters,
                                     long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
                                     const float* q_gain, const float* k_gain, const float* cos_table,
-                                    const float* sin_table, float eps, void* stream) {
+                                    const float* sin_table, float eps, const void* next, long long next_bytes,
+                                    void* stream) {
   // qkv != null: `q` is ignored; the kernel takes the new token's raw projection rows [n, (H + 2 * qkv_kv_heads) * hd],
   // applies bias, QK-norm and the rotation itself, and (qkv_kv_heads == kv_heads) writes the token's key and value
   // into the cache. cos/sin tables, if given, are [positions, hd / 2]: the whole head rotates.
@@ -750,6 +755,8 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
   a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
   a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps;
+  SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "attention (decode): the range to prefetch must be 16-byte aligned");
+  a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   return head_dim == 64 ? launch_decode<64>(a, n_seqs, (cudaStream_t)stream)
                         : launch_decode<128>(a, n_seqs, (cudaStream_t)stream);
 }

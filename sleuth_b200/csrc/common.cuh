@@ -39,6 +39,26 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_wait();
 }
 
+// A range of memory that the kernel after this one will read and that no kernel writes (the next weight matrix).
+// The blocks of a kernel that is given one ask the L2 cache for it, a share each, so that the next kernel finds its
+// weights on the chip: a single-token step leaves the memory system idle more than half of the time, and a kernel
+// that starts early cannot fetch for itself while the blocks in front of it still hold the SM's registers.
+struct NextRead {
+  const char* ptr;
+  long long bytes;
+};
+
+__device__ __forceinline__ void prefetch_share(const NextRead& n, int block, int blocks) {
+  if (n.bytes <= 0) return;
+  const long long share = (((n.bytes + blocks - 1) / blocks) + 127) & ~127LL;      // whole 128-byte lines
+  long long off = (long long)block * share;
+  const long long end = min(n.bytes & ~15LL, off + share);
+  for (; off < end; off += 32768) {
+    const uint32_t size = (uint32_t)min(32768LL, end - off);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(n.ptr + off), "r"(size) : "memory");
+  }
+}
+
 int pdl_mode();                       // 0 off, 1 every kernel, 2 only kernels that prefetch before their wait
 inline bool pdl_enabled() { return pdl_mode() != 0; }
 void note_launch_error(cudaError_t e);

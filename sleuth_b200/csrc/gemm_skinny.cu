@@ -31,6 +31,7 @@ struct SkinnyArgs {
   const __nv_bfloat16* W;   // [N, K]  (kSwiglu: [2 * inter, K], gate rows then up rows)
   void* C;                  // [M, ldc]
   int M, N, K, ldc;         // kSwiglu: N = inter (features of the output)
+  NextRead next;            // what the kernel after this one reads, or nothing
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   // produces X: the memory system is already streaming this layer's weights while the previous kernel finishes.
   pdl_launch_dependents();
   fetch_weights(kb_begin);
+  if (threadIdx.x == 0) prefetch_share(a.next, blockIdx.x, gridDim.x);
   pdl_wait();
   // Adding into the stream: the old values of the outputs this thread will write are asked for now, so that the
   // epilogue does not end on a load from L2.
@@ -298,21 +300,24 @@ extern "C" int slb_gemm_skinny_supported(int M, int N, int K) {
 }
 
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds 2 * N rows, C is [M, N]).
+// next / next_bytes: a read-only range (the next kernel's weights) that the blocks ask into L2, or null.
 extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
-                               void* stream) {
+                               const void* next, long long next_bytes, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 64, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: X and W must be 16-byte aligned");
   SkinnyArgs a{};
   a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
+  a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   return dispatch_skinny<false>(a, mode, (cudaStream_t)stream);
 }
 
 // The same with the RMSNorm of the input fused in: X is the float32 stream [M, K], rows are normalised with
 // `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
 extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
-                                    int K, int ldc, int mode, void* stream) {
+                                    int K, int ldc, int mode, const void* next, long long next_bytes, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16 && K <= kNormMaxK,
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32, at most %d)",
               M, N, K, kNormMaxK);
@@ -321,5 +326,7 @@ extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps
               "gemm_skinny: X, gain and W must be 16-byte aligned");
   SkinnyArgs a{};
   a.Xf = X; a.gain = gain; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
+  a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   return dispatch_skinny<true>(a, mode, (cudaStream_t)stream);
 }

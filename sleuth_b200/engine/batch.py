@@ -45,6 +45,9 @@ class StepBatch:
     host_slots: list = field(default_factory=list)
     max_count: int = 1
     max_len: int = 0
+    # the weight matrix that is read right after the part now running has finished (the next part's first product),
+    # or None: the last kernel of a part may ask the L2 cache for it
+    next_read: torch.Tensor | None = None
 
 
 def _round(n: int) -> int:

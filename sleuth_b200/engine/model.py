@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import BuildContext, ParamDecl, build_layer
+from ..parts.base import BuildContext, ParamDecl, build_layer, lead_weight_of
 from ..parts.ends import LMHead, TokenEmbedding
 from ..parts.spec import ModelSpec
 
@@ -68,9 +68,13 @@ class Model:
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
         self.embedding.forward(b.token_ids, x, b.stream, b.ids_map)
-        for i, e in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for i, e in enumerate(schedule):
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
+            following = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            b.next_read = lead_weight_of(following)
             self.layers[e.layer].forward(x, b, view, ws)
+        b.next_read = None
         if logits.shape[0]:
             self.head.forward(x, b.rows, logits, ws, b.stream)
         ws.release(mark)

@@ -108,6 +108,9 @@ class GQAAttention(Part):
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
                                   s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
 
+    def lead_weight(self):
+        return self.qkv.weight if self.qkv is not None else None
+
     def forward(self, h, x, b, view, ws):
         s = self.spec
         T = h.shape[0]
@@ -144,8 +147,9 @@ class GQAAttention(Part):
             ops.attention_decode(None, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
                                  s.head_dim, view.window, self.scale, splits, scratch, b.stream, qkv=qkv,
                                  qkv_kv_heads=kvh, bias=self.bias, q_gain=self.q_gain, k_gain=self.k_gain,
-                                 cos=cos if rot else None, sin=sin if rot else None, eps=s.qk_norm_eps)
-            self.o.forward(y, into=x, ws=ws, stream=b.stream)
+                                 cos=cos if rot else None, sin=sin if rot else None, eps=s.qk_norm_eps,
+                                 next_read=self.o.weight)
+            self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
             ws.release(mark)
             return
         q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)

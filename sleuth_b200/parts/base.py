@@ -92,6 +92,17 @@ class Part:
     def cache_request(self):
         return None
 
+    def lead_weight(self):
+        """The weight matrix that this part's first product reads, or None. The part that runs before this one may
+        hand it to its last kernel, which then asks the L2 cache for it (``StepBatch.next_read``)."""
+        return None
+
+
+def lead_weight_of(part):
+    """``part.lead_weight()`` for anything that has one, else None."""
+    f = getattr(part, "lead_weight", None)
+    return f() if callable(f) else None
+
 
 _REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "layer": {}}
 

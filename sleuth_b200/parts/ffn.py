@@ -38,6 +38,9 @@ class GatedMLP(Part):
         self.gate_up = Linear(torch.cat([t["gate.weight"], t["up.weight"]], dim=0), self.ctx.dtype)
         self.down = Linear(t["down.weight"], self.ctx.dtype)
 
+    def lead_weight(self):
+        return self.gate_up.weight if self.gate_up is not None else None
+
     def forward(self, h, x, b, ws):
         T = h.shape[0]
         mark = ws.mark()
@@ -46,15 +49,16 @@ class GatedMLP(Part):
             # norm in the product's prologue (when handed the stream), activation in its epilogue
             if (isinstance(h, Normed) and h.gain is not None and FUSE_NORM
                     and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden, norm=True)):
-                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream)
+                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight)
             else:
-                ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
+                ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream,
+                                self.down.weight)
         elif self.ctx.dtype == torch.bfloat16 and linear.use_tc(T, self.spec.intermediate, self.spec.hidden):
             ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
             ops.swiglu(gu, act, b.stream)
-        self.down.forward(act, into=x, ws=ws, stream=b.stream)
+        self.down.forward(act, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
         ws.release(mark)
 
 

@@ -7,7 +7,7 @@ itself is a float32 accumulation into the stream, done by the last product of th
 
 from __future__ import annotations
 
-from .base import BuildContext, Normed, Part, build_ffn, build_mixer, build_norm, register_layer
+from .base import BuildContext, Normed, Part, build_ffn, build_mixer, build_norm, lead_weight_of, register_layer
 from .spec import LayerSpec
 
 
@@ -35,10 +35,16 @@ class PreNormLayer(Part):
     def cache_request(self):
         return self.mixer.cache_request()
 
+    def lead_weight(self):
+        return lead_weight_of(self.mixer)
+
     def forward(self, x, b, view, ws):
         mark = ws.mark()
+        after = getattr(b, "next_read", None)    # what follows this layer
+        b.next_read = lead_weight_of(self.ffn)
         self.mixer.forward(self._input(self.norm1, self.mixer, x, b, ws), x, b, view, ws)
         ws.release(mark)
+        b.next_read = after
         self.ffn.forward(self._input(self.norm2, self.ffn, x, b, ws), x, b, ws)
         ws.release(mark)
 

@@ -93,7 +93,9 @@ class Linear:
         self._wt = self.weight.t()      # a view; the library product reads W^T without a copy
 
     def forward(self, h: torch.Tensor, out: torch.Tensor | None = None, into: torch.Tensor | None = None,
-                ws=None, stream=None, out_dtype: torch.dtype | None = None):
+                ws=None, stream=None, out_dtype: torch.dtype | None = None, next_read: torch.Tensor | None = None):
+        """``next_read``: the weight matrix of the product that follows this one; the weight-streaming kernel asks
+        the L2 cache for it while it runs (the other kernels ignore it)."""
         M = h.shape[0]
         if isinstance(h, Normed):
             if (self.dtype == torch.bfloat16 and h.gain is not None and into is None
@@ -102,7 +104,7 @@ class Linear:
                 if out is None:
                     out = ws.take((M, self.out_features), want)
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, "f32" if want == torch.float32 else "bf16",
-                                     stream)
+                                     stream, next_read)
                 return out
             h = h.tensor()
         if self.dtype == torch.float32:
@@ -115,12 +117,12 @@ class Linear:
             return out
         if use_skinny(M, self.out_features, self.in_features):
             if into is not None:
-                ops.gemm_skinny(h, self.weight, into, "add", stream)
+                ops.gemm_skinny(h, self.weight, into, "add", stream, next_read)
                 return into
             want = out_dtype or (out.dtype if out is not None else self.dtype)
             if out is None:
                 out = ws.take((M, self.out_features), want)
-            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream)
+            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream, next_read)
             return out
         if use_tc(M, self.out_features, self.in_features):
             if into is not None:

@@ -136,7 +136,7 @@ def plain_attention(q, k, v, pos, window, scale):
     return out
 
 
-def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed):
+def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed, next_read=None):
     o = ops()
     gen = torch.Generator().manual_seed(seed)
     lens = [p + c for p, c in zip(pasts, counts)]
@@ -166,7 +166,7 @@ def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed)
         floats = o.decode_scratch_floats(len(counts), heads, hd, splits)
         scratch = torch.full((max(floats, 1),), float("nan"), device=DEV)
         o.attention_decode(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)), d(table),
-                           heads, kv_heads, hd, window, scale, splits, scratch if floats else None)
+                           heads, kv_heads, hd, window, scale, splits, scratch if floats else None, next_read=next_read)
     got = out.cpu().double().view(T, heads, hd)
     assert torch.isfinite(got).all()
     torch.testing.assert_close(got, ref, **(dict(rtol=2e-2, atol=1.5e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)))
@@ -371,6 +371,34 @@ def test_gemm_skinny_gated_activation(M, inter, K):
     act = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
     o.gemm_skinny(x.to(DEV), w.to(DEV), act, "swiglu")
     torch.testing.assert_close(act.cpu().double(), gate * torch.sigmoid(gate) * up, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("next_elems", [8, 72000, 4 << 20, 1001])
+def test_kernels_told_what_is_read_next_compute_the_same(next_elems):
+    """A kernel that is handed the next kernel's weights asks the cache for them and nothing else: its own result is
+    the same bits, whatever the size of the range (a few bytes, no multiple of a cache line, megabytes) and for a
+    range that is not 16-byte aligned (which is not passed on)."""
+    o = ops()
+    g = torch.Generator().manual_seed(next_elems)
+    nxt = torch.randn(next_elems + 1, generator=g).to(torch.bfloat16).to(DEV)
+    nxt = nxt[1:] if next_elems == 1001 else nxt[:next_elems]
+    keep = nxt.clone()
+    for M, N, K in ((3, 40, 96), (8, 4096, 1024)):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+        plain = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        told = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        o.gemm_skinny(x, w, plain, "bf16")
+        o.gemm_skinny(x, w, told, "bf16", next_read=nxt)
+        assert torch.equal(plain, told)
+        gain = torch.ones(K, device=DEV)
+        o.gemm_skinny_norm(x.float(), gain, 1e-6, w, plain, "bf16")
+        o.gemm_skinny_norm(x.float(), gain, 1e-6, w, told, "bf16", next_read=nxt)
+        assert torch.equal(plain, told)
+    run_attention(3, torch.bfloat16, 4, 2, 64, pasts=[5, 300, 64], counts=[1] * 3, window=0, seed=3, next_read=nxt)
+    run_attention(1, torch.bfloat16, 16, 8, 128, pasts=[700], counts=[1], window=0, seed=4, next_read=nxt)
+    torch.cuda.synchronize()
+    assert torch.equal(nxt, keep)
 
 
 def test_gemm_skinny_refuses_what_it_cannot_run():
