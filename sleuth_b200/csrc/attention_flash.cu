@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   const uint32_t sQ = sV + S * TILE;          // [16][HD]
   unsigned char* sQ_ptr = smem + 2 * S * TILE;
 
+  Tracer trace(kTraceDecodeAttention);
   const int seq = blockIdx.z, kh = blockIdx.y;
   const int G = a.heads / a.kv_heads;
   const int row_tiles = (G + 15) / 16;
@@ -405,6 +406,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   // Nothing but read-only loads may come before this wait: the workspace this kernel writes to is shared with
   // kernels that may still be running.
   if (fused) pdl_wait();
+  trace.mark(1);
   if (my_lo <= my_hi) {
     // the newest token's own key and value are not in the cache yet in the fused form: the block whose slice
     // holds the last page works them out itself (warp 0 the key, warp 1 the value) and patches its copy of the page
@@ -537,6 +539,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     }
     cp_async_wait<0>();
   }
+  trace.mark(2);
   // this block has asked for its last page: the next kernel's weights may now use the memory system
   if (tid == 0)
     prefetch_share(a.next, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), gridDim.x * gridDim.y * gridDim.z);
@@ -585,6 +588,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     }
   }
   if (a.splits == 1) return;
+  trace.mark(3);
 
   // The slice that finishes last merges all slices of its (sequence, kv head, row tile): every block publishes
   // its partial result, then takes a ticket; the holder of the last ticket reads them all back, always in slice
@@ -688,6 +692,7 @@ static int launch_decode(const FlashArgs& a, int n_seqs, cudaStream_t s) {
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(attention_flash)
 
 // 1 when the tensor-core kernels take this shape, else 0 (the general kernel then serves it).
 extern "C" int slb_attention_flash_supported(int head_dim, int dtype) {

@@ -59,6 +59,58 @@ __device__ __forceinline__ void prefetch_share(const NextRead& n, int block, int
   }
 }
 
+// A timeline of the kernels, for finding where a step's time goes between and inside its launches. It exists only
+// in a library compiled with -DSLB_TIMELINE (otherwise every line below is empty): thread 0 of each block reads the
+// global nanosecond timer when the block enters, at up to three marks, and when it leaves, and appends one record of
+// six 64-bit words [kind | block << 16 | SM << 48, enter, mark 1, mark 2, mark 3, leave] to a buffer whose first word
+// counts the records. Each file with kernels keeps its own pointer to the buffer (slb_timeline_set_<file>).
+enum TraceKind : int { kTraceEmbed = 1, kTraceNorm, kTraceSkinny, kTraceDecodeAttention, kTraceArgmaxPart, kTraceArgmaxFinal,
+                       kTraceSample, kTraceOther };
+#ifdef SLB_TIMELINE
+static __device__ unsigned long long* g_timeline = nullptr;
+static __device__ unsigned int g_timeline_records = 0;
+#define SLB_TIMELINE_SETTER(file)                                                          \
+  extern "C" int slb_timeline_set_##file(void* buffer, unsigned int records) {            \
+    cudaError_t e = cudaMemcpyToSymbol(slb::g_timeline, &buffer, sizeof(buffer));          \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(slb::g_timeline_records, &records, sizeof(records)); \
+    return e == cudaSuccess ? 0 : 2;                                                       \
+  }
+struct Tracer {
+  unsigned long long t[4];
+  int kind;
+  static __device__ __forceinline__ unsigned long long now() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+  }
+  __device__ __forceinline__ explicit Tracer(int k) : kind(k) {
+    t[0] = now();
+    t[1] = t[2] = t[3] = 0;
+  }
+  __device__ __forceinline__ void mark(int i) {
+    if (threadIdx.x == 0 && threadIdx.y == 0) t[i] = now();
+  }
+  __device__ __forceinline__ ~Tracer() {
+    if (threadIdx.x != 0 || threadIdx.y != 0 || g_timeline == nullptr) return;
+    const unsigned long long leave = now();
+    const unsigned int i = atomicAdd(reinterpret_cast<unsigned int*>(g_timeline), 1u);
+    if (i >= g_timeline_records) return;
+    unsigned int sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    const unsigned long long block = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    unsigned long long* r = g_timeline + 1 + 6ull * i;
+    r[0] = (unsigned long long)kind | (block << 16) | ((unsigned long long)sm << 48);
+    r[1] = t[0]; r[2] = t[1]; r[3] = t[2]; r[4] = t[3]; r[5] = leave;
+  }
+};
+#else
+#define SLB_TIMELINE_SETTER(file)
+struct Tracer {
+  __device__ __forceinline__ explicit Tracer(int) {}
+  __device__ __forceinline__ void mark(int) {}
+};
+#endif
+
 int pdl_mode();                       // 0 off, 1 every kernel, 2 only kernels that prefetch before their wait
 inline bool pdl_enabled() { return pdl_mode() != 0; }
 void note_launch_error(cudaError_t e);

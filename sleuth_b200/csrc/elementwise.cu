@@ -10,7 +10,9 @@ namespace slb {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ map, const TW* __restrict__ table,
                              float* __restrict__ x, int dim, int vocab, float scale) {
+  Tracer trace(kTraceEmbed);
   pdl_enter();
+  trace.mark(1);
   const int t = blockIdx.x;
   int tok = ids[map ? map[t] : t];
   tok = min(max(tok, 0), vocab - 1);
@@ -44,7 +46,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 template <typename TO, int PER_THREAD>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ rows, int dim, float eps) {
+  Tracer trace(kTraceNorm);
   pdl_enter();
+  trace.mark(1);
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
@@ -140,6 +144,7 @@ static int norm_threads(int dim) {
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(elementwise)
 
 extern "C" int slb_embed(const int* ids, const int* map, const void* table, int table_dtype, float* x, int tokens,
                          int dim, int vocab, float scale, void* stream) {

@@ -79,7 +79,9 @@ constexpr int kArgmaxThreads = 256;
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_partial_kernel(const float* __restrict__ logits, long long ld, int limit, float* __restrict__ part_v,
                       int* __restrict__ part_i) {
+  Tracer trace(kTraceArgmaxPart);
   pdl_enter();
+  trace.mark(1);
   __shared__ float best_v[8];
   __shared__ int best_i[8];
   const int r = blockIdx.y, chunk = blockIdx.x;
@@ -114,7 +116,9 @@ argmax_partial_kernel(const float* __restrict__ logits, long long ld, int limit,
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int* __restrict__ out) {
+  Tracer trace(kTraceArgmaxFinal);
   pdl_enter();
+  trace.mark(1);
   const int r = blockIdx.x, lane = threadIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -575,6 +579,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int limit, float t
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(sampling)
 
 extern "C" int slb_penalize(float* logits, long long ld, int rows, int limit, const int* recent, const int* n_recent,
                             int recent_stride, float penalty, const int* banned, const int* n_banned,

@@ -29,6 +29,9 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr"]
+# More flags for a build of one's own, e.g. SLEUTH_B200_NVCC_FLAGS=-DSLB_TIMELINE together with
+# SLEUTH_B200_BUILD_DIR=<another folder> for a library whose kernels record a timeline (kernels/timeline.py).
+NVCC_FLAGS += os.environ.get("SLEUTH_B200_NVCC_FLAGS", "").split()
 LIB_NAME = "libsleuth_b200.so"
 
 _lock = threading.Lock()
