@@ -53,12 +53,14 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   const int r = blockIdx.x;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
   const int n4 = dim >> 2;
-  float4 v[PER_THREAD];
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 v[PER_THREAD], gains[PER_THREAD];      // the gains are asked for with the row, not after the sum
   float ss = 0.0f;
 #pragma unroll
   for (int i = 0; i < PER_THREAD; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    gains[i] = c < n4 ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     ss = fmaf(v[i].x, v[i].x, ss);
     ss = fmaf(v[i].y, v[i].y, ss);
     ss = fmaf(v[i].z, v[i].z, ss);
@@ -66,13 +68,12 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-  const float4* w4 = reinterpret_cast<const float4*>(w);
   TO* o = out + (size_t)r * dim;
 #pragma unroll
   for (int i = 0; i < PER_THREAD; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c >= n4) continue;
-    const float4 g = w4[c];
+    const float4 g = gains[i];
     const float a = (v[i].x * inv) * g.x, b = (v[i].y * inv) * g.y, cc = (v[i].z * inv) * g.z, d = (v[i].w * inv) * g.w;
     if constexpr (sizeof(TO) == 4) {
       reinterpret_cast<float4*>(o)[c] = make_float4(a, b, cc, d);

@@ -77,6 +77,7 @@ __host__ __device__ constexpr int unroll_for(int tiles) { return tiles >= 8 ? 1 
 // while the weight loads still go out in one batch.
 template <int NF, int MODE, bool NORM, int MT>
 __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1 && MT == 1) ? 2 : (((NF == 4 && MT == 1 && !NORM) || (MODE == kSwiglu && NF == 1 && MT <= 2 && !NORM)) ? 3 : 1)) gemm_skinny_kernel(SkinnyArgs a) {
+  Tracer trace(kTraceSkinny);
   constexpr int TILES = MODE == kSwiglu ? 2 * NF : NF;       // weight-row tiles of 8 that a warp multiplies
   constexpr int kUnroll = unroll_for(TILES);
   static_assert(MT == 1 || !NORM, "the fused norm is built for up to 16 rows");
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   fetch_weights(kb_begin);
   if (threadIdx.x == 0) prefetch_share(a.next, blockIdx.x, gridDim.x);
   pdl_wait();
+  trace.mark(1);
   // Adding into the stream: the old values of the outputs this thread will write are asked for now, so that the
   // epilogue does not end on a load from L2.
   constexpr int kOutPerThread = (16 * MT * NF * 8 + kSkinnyWarps * 32 - 1) / (kSkinnyWarps * 32);
@@ -202,6 +204,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
     }
   }
 
+  trace.mark(2);
   // accumulator layout: c0, c1 = (row g, cols 2t, 2t+1); c2, c3 = (row g+8, same cols)
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -293,6 +296,7 @@ static int dispatch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(gemm_skinny)
 
 // 1 when the skinny kernel takes this problem (the caller otherwise uses the library product).
 extern "C" int slb_gemm_skinny_supported(int M, int N, int K) {
