@@ -299,9 +299,12 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
 // One row of the raw q/k/v projection, as csrc/qkv_post.cu treats it: + bias, RMSNorm over the head with `gain`
 // (when given), rotation of the whole head by the token's angles (when tables are given); float32 throughout.
 // Lane l gets channels l * EPL .. l * EPL + EPL - 1; the whole warp must call.
+// The lane's gains, cosines and sines come in registers: they are weights and tables, which the caller fetches before
+// it waits for the kernel that writes `src`.
 template <int HD>
-__device__ __forceinline__ void post_row(const __nv_bfloat16* src, const float* bias, const float* gain, float eps,
-                                         const float* cs, const float* sn, int lane, float (&v)[HD / 32]) {
+__device__ __forceinline__ void post_row(const __nv_bfloat16* src, const float* bias, bool normalise,
+                                         const float (&gain)[HD / 32], float eps, bool rotate, const float (&cs)[HD / 32],
+                                         const float (&sn)[HD / 32], int lane, float (&v)[HD / 32]) {
   constexpr int EPL = HD / 32;
   const int c0 = lane * EPL;
   float ss = 0.0f;
@@ -312,18 +315,18 @@ __device__ __forceinline__ void post_row(const __nv_bfloat16* src, const float* 
     v[e] = x;
     ss = fmaf(x, x, ss);
   }
-  if (gain) {
+  if (normalise) {
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) v[e] = (v[e] * inv) * gain[c0 + e];
+    for (int e = 0; e < EPL; ++e) v[e] = (v[e] * inv) * gain[e];
   }
-  if (cs) {
+  if (rotate) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
       const float partner = __shfl_xor_sync(0xffffffffu, v[e], 16);
       const float other = lane < 16 ? -partner : partner;
-      v[e] = v[e] * cs[(lane & 15) * EPL + e] + other * sn[(lane & 15) * EPL + e];
+      v[e] = v[e] * cs[e] + other * sn[e];
     }
   }
 }
@@ -403,6 +406,17 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
 #pragma unroll
     for (int d = 0; d < S - 1; ++d) fetch(my_lo + d);
   }
+  // The fused form's gains and rotation factors for this lane: weights and tables, asked for before the wait.
+  float q_gain[EPL], k_gain[EPL], cos_l[EPL], sin_l[EPL];
+  const bool norm_q = fused && a.q_gain != nullptr, norm_k = fused && a.k_gain != nullptr;
+  const bool rotate = fused && a.cos_table != nullptr;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    q_gain[e] = norm_q ? a.q_gain[lane * EPL + e] : 1.0f;
+    k_gain[e] = norm_k ? a.k_gain[lane * EPL + e] : 1.0f;
+    cos_l[e] = rotate ? a.cos_table[(size_t)pos * (HD / 2) + (lane & 15) * EPL + e] : 1.0f;
+    sin_l[e] = rotate ? a.sin_table[(size_t)pos * (HD / 2) + (lane & 15) * EPL + e] : 0.0f;
+  }
   // Nothing but read-only loads may come before this wait: the workspace this kernel writes to is shared with
   // kernels that may still be running.
   if (fused) pdl_wait();
@@ -415,13 +429,12 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     if (fused) {
       const int rows_per_token = a.heads + 2 * a.qkv_kv_heads;
       const __nv_bfloat16* raw = a.qkv + (size_t)tok * rows_per_token * HD;
-      const float* cs = a.cos_table ? a.cos_table + (size_t)pos * (HD / 2) : nullptr;
-      const float* sn = a.cos_table ? a.sin_table + (size_t)pos * (HD / 2) : nullptr;
       for (int row = warp; row < 16; row += kFlashThreads / 32) {
         float v[EPL];
         if (row < rows) {
           const int head = head0 + row;
-          post_row<HD>(raw + (size_t)head * HD, a.bias ? a.bias + (size_t)head * HD : nullptr, a.q_gain, a.eps, cs, sn, lane, v);
+          post_row<HD>(raw + (size_t)head * HD, a.bias ? a.bias + (size_t)head * HD : nullptr, norm_q, q_gain, a.eps, rotate,
+                       cos_l, sin_l, lane, v);
         } else {
 #pragma unroll
           for (int e = 0; e < EPL; ++e) v[e] = 0.0f;
@@ -430,8 +443,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       }
       if (owns_last && warp < 2) {
         const int r = a.heads + (warp == 0 ? 0 : a.qkv_kv_heads) + kh;
-        post_row<HD>(raw + (size_t)r * HD, a.bias ? a.bias + (size_t)r * HD : nullptr, warp == 0 ? a.k_gain : nullptr, a.eps,
-                     warp == 0 ? cs : nullptr, sn, lane, new_kv);
+        post_row<HD>(raw + (size_t)r * HD, a.bias ? a.bias + (size_t)r * HD : nullptr, warp == 0 && norm_k, k_gain, a.eps,
+                     warp == 0 && rotate, cos_l, sin_l, lane, new_kv);
         if (rt == 0) {      // one block per (sequence, kv head) stores the row for later steps
           __nv_bfloat16* pool = warp == 0 ? const_cast<__nv_bfloat16*>(a.k_pool) : const_cast<__nv_bfloat16*>(a.v_pool);
           __nv_bfloat16* dst = pool + (((size_t)page_of(page_hi) * a.kv_heads + kh) * 64 + (pos % 64)) * HD + lane * EPL;

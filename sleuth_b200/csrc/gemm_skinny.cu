@@ -124,6 +124,10 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   pdl_launch_dependents();
   fetch_weights(kb_begin);
   if (threadIdx.x == 0) prefetch_share(a.next, blockIdx.x, gridDim.x);
+  if (NORM) {      // the gains are read after the rows' sums of squares: asked into L1 now, they are there by then
+    for (int line = threadIdx.x; line * 32 < a.K; line += kSkinnyWarps * 32)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(a.gain + line * 32));
+  }
   pdl_wait();
   trace.mark(1);
   // Adding into the stream: the old values of the outputs this thread will write are asked for now, so that the
