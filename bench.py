@@ -381,7 +381,11 @@ def main() -> int:
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="run one part only, for profiling (prints that part's numbers, not the full record)")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of --only decode")
+    ap.add_argument("--print-config", action="store_true", help="print the benchmark model's config.json and exit")
     args = ap.parse_args()
+    if args.print_config:
+        print(json.dumps(CONFIG))
+        return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this library runs on a single GPU, --gpus {args.gpus} is not supported")
         return 2
