@@ -59,6 +59,44 @@ __device__ __forceinline__ void prefetch_share(const NextRead& n, int block, int
   }
 }
 
+// The first pages that the single-token attention kernel two launches on will read: that kernel's blocks get onto the
+// SMs only when the blocks of the product in front of it leave, too late to fetch ahead for themselves, while the
+// memory system idles through most of that product. So the product's blocks ask the L2 cache for them: item
+// i = ((sequence * splits + slice) * depth + d) * 2 + (0 key page | 1 value page), the slices cut as
+// attn_decode_kernel cuts them. A page here is a cache page of all kv heads (they lie together).
+struct NextPages {
+  const char* k_pool;        // null: nothing to do
+  const char* v_pool;
+  const int* block_table;    // [n_seqs, table_stride]
+  const int* past;           // [n_seqs] position of each sequence's new token
+  long long page_bytes;
+  int table_stride, n_seqs, splits, depth, window;
+};
+
+// The whole warp calls; every lane works out the same page, lanes 0.. ask for 32 KB of it each.
+__device__ __forceinline__ void prefetch_page_item(const NextPages& p, int item, int lane) {
+  const int which = item & 1;
+  int rest = item >> 1;
+  const int d = rest % p.depth;
+  rest /= p.depth;
+  const int slice = rest % p.splits, seq = rest / p.splits;
+  if (seq >= p.n_seqs) return;
+  const int pos = p.past[seq];
+  const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int page_lo = key_lo / 64, page_hi = pos / 64;
+  const int per = (page_hi - page_lo + 1 + p.splits - 1) / p.splits;
+  const int my_lo = page_lo + slice * per, my_hi = min(page_hi, my_lo + per - 1);
+  const int page = my_lo + d;
+  if (page > my_hi || page >= p.table_stride) return;
+  const int phys = p.block_table[(size_t)seq * p.table_stride + page];
+  const char* base = (which ? p.v_pool : p.k_pool) + (size_t)phys * p.page_bytes;
+  const long long off = (long long)lane * 32768;
+  if (off < p.page_bytes) {
+    const uint32_t size = (uint32_t)min(32768LL, (p.page_bytes - off) & ~15LL);
+    if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(size) : "memory");
+  }
+}
+
 // A timeline of the kernels, for finding where a step's time goes between and inside its launches. It exists only
 // in a library compiled with -DSLB_TIMELINE (otherwise every line below is empty): thread 0 of each block reads the
 // global nanosecond timer when the block enters, at up to three marks, and when it leaves, and appends one record of

@@ -32,6 +32,7 @@ struct SkinnyArgs {
   void* C;                  // [M, ldc]
   int M, N, K, ldc;         // kSwiglu: N = inter (features of the output)
   NextRead next;            // what the kernel after this one reads, or nothing
+  NextPages pages;          // cache pages that the attention kernel after this one reads first, or nothing
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -124,6 +125,10 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
   pdl_launch_dependents();
   fetch_weights(kb_begin);
   if (threadIdx.x == 0) prefetch_share(a.next, blockIdx.x, gridDim.x);
+  if (a.pages.k_pool != nullptr && warp == kSkinnyWarps - 1) {
+    const int items = a.pages.n_seqs * a.pages.splits * a.pages.depth * 2;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) prefetch_page_item(a.pages, item, lane);
+  }
   if (NORM) {      // the gains are read after the rows' sums of squares: asked into L1 now, they are there by then
     for (int line = threadIdx.x; line * 32 < a.K; line += kSkinnyWarps * 32)
       asm volatile("prefetch.global.L1 [%0];" ::"l"(a.gain + line * 32));
@@ -309,8 +314,21 @@ extern "C" int slb_gemm_skinny_supported(int M, int N, int K) {
 
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds 2 * N rows, C is [M, N]).
 // next / next_bytes: a read-only range (the next kernel's weights) that the blocks ask into L2, or null.
+// pages: null, or what the attention kernel that follows this product will read first (see NextPages).
+static int take_pages(SkinnyArgs& a, const NextPages* pages) {
+  a.pages = NextPages{};
+  if (pages == nullptr || pages->k_pool == nullptr) return 0;
+  SLB_REQUIRE(pages->v_pool && pages->block_table && pages->past && pages->page_bytes > 0 && pages->page_bytes % 16 == 0 &&
+              (uintptr_t)pages->k_pool % 16 == 0 && (uintptr_t)pages->v_pool % 16 == 0 && pages->table_stride > 0 &&
+              pages->n_seqs > 0 && pages->splits > 0 && pages->depth > 0 && pages->window >= 0 &&
+              pages->page_bytes <= 32 * 32768,
+              "gemm_skinny: the description of the pages to prefetch is incomplete");
+  a.pages = *pages;
+  return 0;
+}
+
 extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
-                               const void* next, long long next_bytes, void* stream) {
+                               const void* next, long long next_bytes, const NextPages* pages, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 64, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
@@ -319,13 +337,15 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
   a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
+  if (int rc = take_pages(a, pages)) return rc;
   return dispatch_skinny<false>(a, mode, (cudaStream_t)stream);
 }
 
 // The same with the RMSNorm of the input fused in: X is the float32 stream [M, K], rows are normalised with
 // `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
 extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
-                                    int K, int ldc, int mode, const void* next, long long next_bytes, void* stream) {
+                                    int K, int ldc, int mode, const void* next, long long next_bytes,
+                                    const NextPages* pages, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16 && K <= kNormMaxK,
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32, at most %d)",
               M, N, K, kNormMaxK);
@@ -336,5 +356,6 @@ extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps
   a.Xf = X; a.gain = gain; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
+  if (int rc = take_pages(a, pages)) return rc;
   return dispatch_skinny<true>(a, mode, (cudaStream_t)stream);
 }

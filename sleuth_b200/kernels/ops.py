@@ -10,6 +10,7 @@ is (sleuth/forge/model/attention.py:106-108,157; mlp.py:38-41; transformer.py:30
 
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -281,7 +282,31 @@ def _nbytes(t) -> int:
     return t.numel() * t.element_size()
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None, next_read=None) -> None:
+class _NextPages(ctypes.Structure):
+    _fields_ = [("k_pool", ctypes.c_void_p), ("v_pool", ctypes.c_void_p), ("block_table", ctypes.c_void_p),
+                ("past", ctypes.c_void_p), ("page_bytes", ctypes.c_longlong), ("table_stride", ctypes.c_int),
+                ("n_seqs", ctypes.c_int), ("splits", ctypes.c_int), ("depth", ctypes.c_int), ("window", ctypes.c_int)]
+
+
+def next_pages(k_pool, v_pool, block_table, past, splits: int, window: int, depth: int = 2):
+    """What a few-rows product hands its kernel as ``next_pages`` when ``attention_decode`` with these arguments
+    follows it: the product's blocks then ask the L2 cache for the first ``depth`` pages of every slice."""
+    if not PREFETCH:
+        return None
+    _cuda(k_pool, v_pool, block_table, past)
+    page_bytes = k_pool[0].numel() * k_pool.element_size()
+    if page_bytes > 32 * 32768 or page_bytes % 16:
+        return None
+    return _NextPages(k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(), past.data_ptr(), page_bytes,
+                      block_table.shape[1], block_table.shape[0], int(splits), int(depth), int(window))
+
+
+def _pages_arg(pages):
+    return None if pages is None else ctypes.addressof(pages)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None, next_read=None,
+                next_pages=None) -> None:
     """out = x[M, K] @ w^T for M <= 16 (bfloat16 in, float32 accumulation). mode: "bf16" / "f32" store,
     "add" adds into a float32 ``out``, "swiglu" takes w = [gate rows; up rows] and stores silu(gate) * up.
     ``next_read``: a weight tensor that the kernel after this one reads; the blocks ask the L2 cache for it."""
@@ -292,11 +317,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, 
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny: output dtype")
     lib().call("slb_gemm_skinny", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode], _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
-               stream if stream is not None else current_stream())
+               _pages_arg(next_pages), stream if stream is not None else current_stream())
 
 
 def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor, mode: str,
-                     stream=None, next_read=None) -> None:
+                     stream=None, next_read=None, next_pages=None) -> None:
     """``gemm_skinny`` on rmsnorm(x; gain, eps): x is the float32 stream [M, K], normalised inside the kernel."""
     _cuda(x, gain, w, out)
     M, K = x.shape
@@ -306,7 +331,8 @@ def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.T
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny_norm: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny_norm: output dtype")
     lib().call("slb_gemm_skinny_norm", _p(x), _p(gain), float(eps), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode],
-               _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read), stream if stream is not None else current_stream())
+               _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read), _pages_arg(next_pages),
+               stream if stream is not None else current_stream())
 
 
 def tc_supported(M: int, N: int, K: int) -> bool:

@@ -137,11 +137,16 @@ class GQAAttention(Part):
             self.o.forward(y, into=x, ws=ws, stream=b.stream)
             ws.release(mark)
             return
-        qkv = self.qkv.forward(h, ws=ws, stream=b.stream)
-        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
-        if flash and b.max_count == 1 and rot in (0, s.head_dim) and (writes or s.reads_shared_kv):
-            # one token per sequence: the attention kernel post-processes q/k/v itself and appends to the cache
+        single = flash and b.max_count == 1 and rot in (0, s.head_dim) and (writes or s.reads_shared_kv)
+        pages = None
+        if single:
             splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
+            # the attention kernel gets onto the SMs too late to fetch ahead: the projection asks L2 for its first pages
+            pages = ops.next_pages(view.k_pool, view.v_pool, table, b.past, splits, view.window)
+        qkv = self.qkv.forward(h, ws=ws, stream=b.stream, next_pages=pages)
+        y = ws.take((T, s.heads * s.head_dim), self.ctx.dtype)
+        if single:
+            # one token per sequence: the attention kernel post-processes q/k/v itself and appends to the cache
             floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
             scratch = ws.take((floats,), torch.float32) if floats else None
             ops.attention_decode(None, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,

@@ -93,9 +93,11 @@ class Linear:
         self._wt = self.weight.t()      # a view; the library product reads W^T without a copy
 
     def forward(self, h: torch.Tensor, out: torch.Tensor | None = None, into: torch.Tensor | None = None,
-                ws=None, stream=None, out_dtype: torch.dtype | None = None, next_read: torch.Tensor | None = None):
+                ws=None, stream=None, out_dtype: torch.dtype | None = None, next_read: torch.Tensor | None = None,
+                next_pages=None):
         """``next_read``: the weight matrix of the product that follows this one; the weight-streaming kernel asks
-        the L2 cache for it while it runs (the other kernels ignore it)."""
+        the L2 cache for it while it runs (the other kernels ignore it). ``next_pages``: the same for the cache pages
+        that a single-token attention kernel right behind this product reads first (``ops.next_pages``)."""
         M = h.shape[0]
         if isinstance(h, Normed):
             if (self.dtype == torch.bfloat16 and h.gain is not None and into is None
@@ -104,7 +106,7 @@ class Linear:
                 if out is None:
                     out = ws.take((M, self.out_features), want)
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, "f32" if want == torch.float32 else "bf16",
-                                     stream, next_read)
+                                     stream, next_read, next_pages)
                 return out
             h = h.tensor()
         if self.dtype == torch.float32:
@@ -122,7 +124,7 @@ class Linear:
             want = out_dtype or (out.dtype if out is not None else self.dtype)
             if out is None:
                 out = ws.take((M, self.out_features), want)
-            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream, next_read)
+            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream, next_read, next_pages)
             return out
         if use_tc(M, self.out_features, self.in_features):
             if into is not None:

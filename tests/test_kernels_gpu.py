@@ -395,6 +395,22 @@ def test_kernels_told_what_is_read_next_compute_the_same(next_elems):
         o.gemm_skinny_norm(x.float(), gain, 1e-6, w, plain, "bf16")
         o.gemm_skinny_norm(x.float(), gain, 1e-6, w, told, "bf16", next_read=nxt)
         assert torch.equal(plain, told)
+    # the same for the cache pages of an attention kernel that follows: sequences of 1, 64 and 700 keys, with and
+    # without a window, more slices than pages, a table with unused entries
+    kv_heads, hd = 2, 64
+    lens = [1, 64, 700]
+    pool = torch.randn(16, kv_heads, 64, hd, generator=g).to(torch.bfloat16).to(DEV)
+    vpool = pool.clone()
+    table = torch.full((3, 12), 15, dtype=torch.int32)
+    table[0, 0], table[1, :2], table[2, :11] = 0, torch.tensor([1, 2]), torch.arange(3, 14)
+    past = torch.tensor([n - 1 for n in lens], dtype=torch.int32).to(DEV)
+    for splits, window in ((1, 0), (5, 0), (16, 100)):
+        pages = o.next_pages(pool, vpool, table.to(DEV), past, splits, window)
+        o.gemm_skinny(x, w, told, "bf16", next_pages=pages)
+        o.gemm_skinny(x, w, plain, "bf16")
+        assert torch.equal(plain, told)
+    torch.cuda.synchronize()
+    assert torch.equal(pool, vpool)
     run_attention(3, torch.bfloat16, 4, 2, 64, pasts=[5, 300, 64], counts=[1] * 3, window=0, seed=3, next_read=nxt)
     run_attention(1, torch.bfloat16, 16, 8, 128, pasts=[700], counts=[1], window=0, seed=4, next_read=nxt)
     torch.cuda.synchronize()
