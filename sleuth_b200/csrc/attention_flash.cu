@@ -606,13 +606,18 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   // The slice that finishes last merges all slices of its (sequence, kv head, row tile): every block publishes
   // its partial result, then takes a ticket; the holder of the last ticket reads them all back, always in slice
   // order, so the sum does not depend on which block that is. It leaves the counter at zero for the next launch.
-  __threadfence();
+  // The block's stores are ordered before the barrier, the barrier before thread 0's ticket, and the ticket is one
+  // release-acquire operation at device scope: what the blocks with earlier tickets stored is visible to this thread
+  // after it, and through the second barrier to the whole block.
   __syncthreads();
   int* counter = a.counters + ((size_t)seq * a.kv_heads + kh) * row_tiles + rt;
-  if (tid == 0) ticket = atomicAdd(counter, 1);
+  if (tid == 0) {
+    int got;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(got) : "l"(counter) : "memory");
+    ticket = got;
+  }
   __syncthreads();
   if (ticket != a.splits - 1) return;
-  __threadfence();
   for (int idx = tid; idx < rows * HD; idx += kFlashThreads) {
     const int row = idx / HD, d = idx % HD;
     const int head = head0 + row;
