@@ -273,13 +273,18 @@ def skinny_supported(M: int, N: int, K: int, norm: bool = False) -> bool:
 # SLEUTH_B200_PREFETCH=0: kernels are not told what the kernel after them reads (for comparisons; measured on a
 # B200 at batch 8: 1.055 ms a step with the hints, 1.073 ms without; no difference at batch 1).
 PREFETCH = os.environ.get("SLEUTH_B200_PREFETCH", "1") != "0"
+# No hint for a matrix of more than a quarter of the 126 MB L2: it would push out what it is meant to keep, and a
+# product that large is bound by memory bandwidth, not by latency (hidden 4,096, one row: 1.40 ms a step with this
+# limit, 1.57 ms without; hidden 2,048: 1.31 against 1.27 ms).
+PREFETCH_MOST = 32 << 20
 
 
 def _nbytes(t) -> int:
     """Bytes of a range handed to a kernel as its ``next_read``: 0 (no hint) unless it is one aligned piece of memory."""
     if t is None or not PREFETCH or not t.is_contiguous() or t.data_ptr() % 16:
         return 0
-    return t.numel() * t.element_size()
+    n = t.numel() * t.element_size()
+    return n if n <= PREFETCH_MOST else 0
 
 
 class _NextPages(ctypes.Structure):
