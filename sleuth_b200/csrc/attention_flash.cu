@@ -107,6 +107,7 @@ __device__ __forceinline__ void load_page(unsigned char* smem_base, uint32_t dst
 }
 
 constexpr int kFlashThreads = 128;
+constexpr int kMergeBatch = 16;      // slices whose partial results the merging block asks for at once
 
 // ------------------------------------------------------------------------------------ prefill ----
 template <int HD>
@@ -622,13 +623,13 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     const int row = idx / HD, d = idx % HD;
     const int head = head0 + row;
     const size_t base = ((size_t)seq * a.heads + head) * a.splits;
-    // eight slices at a time, all loads issued before any is used (they come from L2, one latency per batch);
+    // sixteen slices at a time, all loads issued before any is used (they come from L2, one latency per batch);
     // a running maximum rescales what has been summed, as in the attention loop itself
     float m = -INFINITY, l = 0.0f, acc = 0.0f;
-    for (int s0 = 0; s0 < a.splits; s0 += 8) {
-      float pm[8], pl[8], po[8];
+    for (int s0 = 0; s0 < a.splits; s0 += kMergeBatch) {
+      float pm[kMergeBatch], pl[kMergeBatch], po[kMergeBatch];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < kMergeBatch; ++j) {
         const bool live = s0 + j < a.splits;
         pm[j] = live ? __ldcg(a.part_ml + (base + s0 + j) * 2) : -INFINITY;
         pl[j] = live ? __ldcg(a.part_ml + (base + s0 + j) * 2 + 1) : 0.0f;
@@ -636,13 +637,13 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       }
       float m_new = m;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m_new = fmaxf(m_new, pm[j]);
+      for (int j = 0; j < kMergeBatch; ++j) m_new = fmaxf(m_new, pm[j]);
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float keep = exp2f(m - m_use);
       l *= keep;
       acc *= keep;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < kMergeBatch; ++j) {
         const float f = exp2f(pm[j] - m_use);
         l += pl[j] * f;
         acc += po[j] * f;
