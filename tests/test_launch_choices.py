@@ -44,3 +44,21 @@ def test_norm_is_fused_only_where_it_was_measured_to_pay():
     assert not linear.use_skinny(16, 4096, 2048, norm=True)      # too many rows for that width
     assert linear.use_skinny(16, 6144, 4096)                     # the plain product still takes it
     assert not linear.use_skinny(linear.SKINNY_ROWS + 1, 1024, 1024)
+
+
+def test_timeline_groups_block_records_into_launches():
+    """Two launches of one kind (the second reuses block numbers), one of another kind in between, out of order."""
+    from sleuth_b200.kernels import timeline
+    rec = lambda kind, block, enter, go, m2, leave: {"kind": kind, "block": block, "sm": block, "enter": enter,
+                                                      "marks": [go, m2, 0], "leave": leave}
+    records = [rec("gemm_skinny", 0, 100, 900, 1500, 1700), rec("gemm_skinny", 1, 120, 910, 1600, 1800),
+               rec("rmsnorm", 0, 1900, 1950, 0, 2500),
+               rec("gemm_skinny", 0, 2000, 2900, 3300, 3500), rec("gemm_skinny", 1, 2600, 2950, 3400, 3600)]
+    records.sort(key=lambda r: r["enter"])
+    out = timeline.launches(records)
+    assert [(L["kind"], L["blocks"]) for L in out] == [("gemm_skinny", 2), ("rmsnorm", 1), ("gemm_skinny", 2)]
+    first, norm, second = out
+    assert (first["first_enter"], first["last_enter"], first["first_go"], first["last_go"]) == (100, 120, 900, 910)
+    assert (first["last_mark2"], first["first_leave"], first["last_leave"]) == (1600, 1700, 1800)
+    assert norm["last_mark2"] == 0 and norm["last_leave"] == 2500
+    assert (second["first_enter"], second["last_enter"], second["last_leave"]) == (2000, 2600, 3600)
