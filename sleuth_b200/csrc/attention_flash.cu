@@ -571,12 +571,11 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = g + 8 * h;
+    if (row >= rows) continue;         // only the rows that exist are read back (two of sixteen with two heads a group)
     if (t4 == 0) { mm[warp * 16 + row] = m_r[h]; ml[warp * 16 + row] = l_r[h]; }
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      mo[(warp * 16 + row) * HD + i * 8 + 2 * t4] = o[i][2 * h];
-      mo[(warp * 16 + row) * HD + i * 8 + 2 * t4 + 1] = o[i][2 * h + 1];
-    }
+    for (int i = 0; i < HD / 8; ++i)
+      *reinterpret_cast<float2*>(mo + (warp * 16 + row) * HD + i * 8 + 2 * t4) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
   }
   __syncthreads();
   for (int idx = tid; idx < rows * HD; idx += kFlashThreads) {
