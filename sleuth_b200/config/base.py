@@ -6,9 +6,10 @@ errors; keys the dataclass does not name are kept aside in ``unread`` (a ``confi
 bookkeeping such as ``transformers_version`` that no formula needs), so nothing is silently
 misread and nothing harmless is refused.
 
-The strict dict -> dataclass idea follows sleuth/config.py:57-107 (type coercion where an int may
-stand for a float, an error that names the key); the key set and defaults of the Qwen3 family are
-those of sleuth/formats/hf.py:83-118.
+The reference reads its own TOML run configurations as strictly (sleuth/config.py:57-107: unknown
+keys refused with a hint, an integer accepted where a float is wanted, errors that name the key);
+here the rules are a table by annotation (``_PLAIN``). The key set and defaults of the Qwen3 family
+are those of sleuth/formats/hf.py:83-118.
 """
 
 from __future__ import annotations
@@ -26,43 +27,49 @@ class ConfigError(ValueError):
     """config.json is missing a key, has a value of the wrong type, or asks for something unsupported."""
 
 
-def _coerce(val: Any, typ: Any, name: str) -> Any:
-    origin = typing.get_origin(typ)
-    if origin in (typing.Union, types.UnionType):
-        errors = []
-        for a in typing.get_args(typ):
-            try:
-                return _coerce(val, a, name)
-            except ConfigError as e:
-                errors.append(str(e))
-        raise ConfigError(f"{name}: {val!r} does not match {typ}")
-    if typ is type(None):
-        if val is not None:
-            raise ConfigError(f"{name}: expected null, got {val!r}")
-        return None
-    if typ is float:
-        if isinstance(val, bool) or not isinstance(val, (int, float)):
-            raise ConfigError(f"{name}: expected a number, got {val!r}")
-        return float(val)
-    if typ is int:
-        if isinstance(val, bool) or not isinstance(val, int):
-            raise ConfigError(f"{name}: expected an integer, got {val!r}")
-        return val
-    if typ is bool:
-        if not isinstance(val, bool):
-            raise ConfigError(f"{name}: expected true or false, got {val!r}")
-        return val
-    if typ is str:
-        if not isinstance(val, str):
-            raise ConfigError(f"{name}: expected a string, got {val!r}")
-        return val
-    if origin in (list, tuple):
-        if not isinstance(val, (list, tuple)):
-            raise ConfigError(f"{name}: expected a list, got {val!r}")
-        args = typing.get_args(typ)
-        inner = args[0] if args else Any
-        return tuple(_coerce(v, inner, f"{name}[{i}]") if inner is not Any else v for i, v in enumerate(val))
-    return val
+def _is_number(v) -> bool:
+    return isinstance(v, (int, float)) and not isinstance(v, bool)
+
+
+def _is_integer(v) -> bool:
+    return isinstance(v, int) and not isinstance(v, bool)
+
+
+# What a JSON value must be for each plain annotation: (test, the words the error uses, how the value is kept).
+# JSON has one number type, so an integer may stand where a float is wanted; nothing else converts.
+_PLAIN = {
+    float: (_is_number, "a number", float),
+    int: (_is_integer, "an integer", lambda v: v),
+    bool: (lambda v: isinstance(v, bool), "true or false", lambda v: v),
+    str: (lambda v: isinstance(v, str), "a string", lambda v: v),
+    type(None): (lambda v: v is None, "null", lambda v: v),
+}
+
+
+def _alternatives(annotation) -> tuple:
+    """The member types of ``X | Y`` / ``Optional[X]``; the annotation itself otherwise."""
+    if typing.get_origin(annotation) in (typing.Union, types.UnionType):
+        return typing.get_args(annotation)
+    return (annotation,)
+
+
+def _fit(value: Any, annotation: Any, where: str) -> Any:
+    """``value`` as the field annotated ``annotation`` keeps it, or a ConfigError naming ``where``."""
+    wanted = []
+    for alt in _alternatives(annotation):
+        if alt in _PLAIN:
+            test, words, keep = _PLAIN[alt]
+            if test(value):
+                return keep(value)
+            wanted.append(words)
+        elif typing.get_origin(alt) in (list, tuple):
+            if isinstance(value, (list, tuple)):
+                item = (typing.get_args(alt) or (Any,))[0]
+                return tuple(_fit(v, item, f"{where}[{i}]") for i, v in enumerate(value))
+            wanted.append("a list")
+        else:
+            return value                # Any, or an annotation this reader has no rule for: taken as it is
+    raise ConfigError(f"{where}: expected {' or '.join(wanted)}, got {value!r}")
 
 
 def read_fields(cls, d: dict, where: str = "config.json"):
@@ -79,7 +86,7 @@ def read_fields(cls, d: dict, where: str = "config.json"):
         if not f.init:
             continue
         if f.name in d and d[f.name] is not None:
-            kwargs[f.name] = _coerce(d[f.name], hints[f.name], f"{where}: {f.name}")
+            kwargs[f.name] = _fit(d[f.name], hints[f.name], f"{where}: {f.name}")
         elif f.name in d and d[f.name] is None and _allows_none(hints[f.name]):
             kwargs[f.name] = None
         elif f.default is dataclasses.MISSING and f.default_factory is dataclasses.MISSING:
@@ -92,8 +99,7 @@ def read_fields(cls, d: dict, where: str = "config.json"):
 
 
 def _allows_none(typ) -> bool:
-    origin = typing.get_origin(typ)
-    return origin in (typing.Union, types.UnionType) and type(None) in typing.get_args(typ)
+    return type(None) in _alternatives(typ)
 
 
 def read_config_json(folder) -> dict:

@@ -38,29 +38,53 @@ def uniforms(seed: int, requests, step_of) -> np.ndarray:
     return np.asarray([uniform(seed, r, s) for r, s in zip(requests, step_of)], dtype=np.float32).clip(0.0, _BELOW_ONE)
 
 
+class _Node:
+    """A node of the phrase trie: children by token, and the tokens seen right after this phrase when it is n-1 long."""
+    __slots__ = ("next", "after")
+
+    def __init__(self):
+        self.next: dict[int, "_Node"] = {}
+        self.after: set[int] = set()
+
+
 class NgramBlocker:
-    """Remembers, for every (n-1)-token phrase seen, the tokens that followed it, so that the token
-    completing a seen n-gram can be banned. Incremental: each token costs one dictionary update.
-    The prompt counts. (Behaviour of sleuth/forge/infer/sampling.py:36-64.)"""
+    """Bans the tokens that would complete an n-gram the sequence already holds (the prompt counts).
+
+    The phrases of n-1 tokens seen so far form a trie; a node at depth n-1 keeps the tokens that have
+    followed its phrase. ``_open`` holds, for each length 0..n-2, the node reached by the most recent
+    tokens of that length, so a new token extends every open phrase by one step and the node that the
+    last n-1 tokens reach is always at hand: one token costs n-1 dictionary steps, a query none.
+    The rule itself is the reference's (sleuth/forge/infer/sampling.py:36-64): with n = 1 every token
+    seen is banned, with n <= 0 nothing is."""
 
     def __init__(self, n: int, ids=()):
-        self.n = n
-        self.ids: list[int] = []
-        self.followers: dict[tuple, set] = {}
+        self.n = int(n)
+        self._root = _Node()
+        self._open: list[_Node] = [self._root]      # _open[k]: the node of the last k tokens (k < n - 1)
+        self._last: _Node | None = self._root if self.n == 1 else None   # the node of the last n-1 tokens
         for t in ids:
             self.add(t)
 
     def add(self, token: int) -> None:
-        self.ids.append(int(token))
-        if self.n > 0 and len(self.ids) >= self.n:
-            key = tuple(self.ids[len(self.ids) - self.n:-1])
-            self.followers.setdefault(key, set()).add(int(token))
+        if self.n <= 0:
+            return
+        token = int(token)
+        if self._last is not None:
+            self._last.after.add(token)              # the last n-1 tokens were followed by this one
+        if self.n == 1:
+            return
+        grown = [self._root]
+        for node in self._open:                      # every open phrase takes the token
+            child = node.next.get(token)
+            if child is None:
+                child = node.next[token] = _Node()
+            grown.append(child)
+        full = grown[self.n - 1] if len(grown) >= self.n else None
+        self._open = grown[:self.n - 1]
+        self._last = full
 
     def banned(self) -> list[int]:
-        if self.n <= 0 or len(self.ids) < self.n - 1:
-            return []
-        key = tuple(self.ids[len(self.ids) - (self.n - 1):]) if self.n > 1 else ()
-        return sorted(self.followers.get(key, ()))
+        return sorted(self._last.after) if self.n > 0 and self._last is not None else []
 
 
 def recent_window(context: list[int], repeat_last_n: int) -> list[int]:
