@@ -140,6 +140,36 @@ class CacheBook:
                 need[gi] += max(0, pages_for(n) - lo - have)
         return need
 
+    def peak_pages_needed(self, chunks) -> list[int]:
+        """The most pages each group's pool must still give out at any moment while ``chunks`` run one after
+        another, each a ``(slots, new_lengths)`` pair that is grown and then committed. A windowed group hands
+        pages back as its sequences move on, so its peak can lie below what the final lengths alone suggest.
+        Nothing is changed: the run is only played through on copies of the counts."""
+        peaks = []
+        for g in self.groups:
+            first = {}
+            have = {}
+            out = peak = 0
+            for slots, new_lengths in chunks:
+                for s, n in zip(slots, new_lengths):
+                    if s not in first:
+                        first[s] = int(g.first_page[s])
+                        have[s] = int((g.table[s] >= 0).sum())
+                    take = max(0, pages_for(n) - first[s] - have[s])
+                    have[s] += take
+                    out += take
+                peak = max(peak, out)
+                if g.window:
+                    for s, n in zip(slots, new_lengths):
+                        keep_from = max(0, n - g.window + 1) // PAGE_TOKENS
+                        if keep_from > first[s]:
+                            back = min(have[s], keep_from - first[s])
+                            have[s] -= back
+                            out -= back
+                            first[s] = keep_from
+            peaks.append(peak)
+        return peaks
+
     def grow(self, slots, new_lengths) -> None:
         """Take the pages for ``new_lengths`` (all or nothing) without changing the lengths yet."""
         for s, n in zip(slots, new_lengths):

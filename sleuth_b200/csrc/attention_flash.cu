@@ -53,6 +53,7 @@ struct FlashArgs {
   const float* sin_table;
   float eps;
   int qkv_kv_heads;             // key/value heads present in qkv (0: this layer reads another layer's cache)
+  int pages_after_wait;         // 1: no cache page is asked for before the kernel in front has completed (see the kernel)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -355,10 +356,15 @@ template <int HD, int S>
 __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a) {
   // Fused form: the keys and values of earlier tokens, the block table and the lengths were all written before the
   // kernel that precedes this one began, so pages are requested before the wait for that kernel (which produces
-  // only the raw projection of the new token). Unfused form: the preceding kernel writes the newest cache row.
+  // only the raw projection of the new token). That holds when this kernel itself appends the token's key and value,
+  // and only while an ordinary launch (one that does not start early: a norm, the embedding) stands somewhere
+  // between this step's earlier cache writers and this kernel, which is the case when only the prefetching kernels
+  // start early. The launcher sets pages_after_wait where it does not hold: the unfused form (the kernel in front
+  // writes the newest cache row), an entry that another layer application of this step wrote, and the mode in which
+  // every kernel starts early.
   const bool fused = a.qkv != nullptr;
   pdl_launch_dependents();
-  if (!fused) pdl_wait();
+  if (a.pages_after_wait) pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE = 64 * HD * 2;
   constexpr int EPL = HD / 32;
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   }
   // Nothing but read-only loads may come before this wait: the workspace this kernel writes to is shared with
   // kernels that may still be running.
-  if (fused) pdl_wait();
+  if (!a.pages_after_wait) pdl_wait();
   trace.mark(1);
   if (my_lo <= my_hi) {
     // the newest token's own key and value are not in the cache yet in the fused form: the block whose slice
@@ -673,9 +679,7 @@ static int launch_prefill(const FlashArgs& a, int n_seqs, int max_count, cudaStr
 // Two page buffers instead of three when that makes all blocks resident at once: with three buffers two blocks fit
 // an SM (296 in all), with two buffers three (444).
 static int decode_stages(long long blocks) {
-  int sms = 148, dev = 0;
-  cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const int sms = sm_count();
   return (blocks > 2ll * sms && blocks <= 3ll * sms) ? 2 : 3;
 }
 
@@ -778,6 +782,7 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
   a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
   a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps;
+  a.pages_after_wait = (qkv == nullptr || qkv_kv_heads == 0 || pdl_mode() == 1) ? 1 : 0;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "attention (decode): the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   return head_dim == 64 ? launch_decode<64>(a, n_seqs, (cudaStream_t)stream)

@@ -149,6 +149,7 @@ struct Tracer {
 };
 #endif
 
+int sm_count();                       // streaming multiprocessors of the current device (148 on a B200)
 int pdl_mode();                       // 0 off, 1 every kernel, 2 only kernels that prefetch before their wait
 inline bool pdl_enabled() { return pdl_mode() != 0; }
 void note_launch_error(cudaError_t e);

@@ -197,7 +197,7 @@ extern "C" int slb_add(float* x, const void* delta, int delta_dtype, long long n
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   if (delta_dtype == kF32)
     launch(add_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, x, (const float*)delta, (size_t)n);
   else if (delta_dtype == kBF16)
@@ -214,11 +214,11 @@ extern "C" int slb_swiglu(const void* gu, void* act, int dtype, int tokens, int 
   const size_t total = (size_t)tokens * inter;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   if (dtype == kBF16 && inter % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)act % 16 == 0)) {
     const size_t total8 = total / 8;
     size_t b8 = (total8 + threads - 1) / threads;
-    if (b8 > 148 * 32) b8 = 148 * 32;
+    if (b8 > sm_count() * 32) b8 = sm_count() * 32;
     launch(swiglu_bf16x8_kernel, dim3((int)b8), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inter, total8);
     return check_launch("swiglu");
   }

@@ -39,7 +39,20 @@ int check_launch(const char* what) {
   return 0;
 }
 
+int sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  static int cached[64] = {0};
+  if (cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+  cached[dev] = sms;
+  return sms;
+}
+
 }  // namespace slb
+
+// Streaming multiprocessors of the current device: the launch heuristics on both sides of the binding count with it.
+extern "C" int slb_sm_count() { return slb::sm_count(); }
 
 extern "C" const char* slb_last_error() { return slb::g_message; }
 

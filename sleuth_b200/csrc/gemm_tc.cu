@@ -423,16 +423,6 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-static int sm_count() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
-  return sms;
-}
-
 template <int BN, bool QKV = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s, const TcQkv& qa = TcQkv{}) {
   constexpr int kStages = tc_stages(BN);

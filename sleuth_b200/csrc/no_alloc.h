@@ -22,6 +22,9 @@
 //     ordering between them) race on it and must not be made; calls ordered on one stream are fine.
 //   * Nothing has to be cleared between calls: each call's second stage reads only slots that its own first
 //     stage wrote, so what an earlier call left behind is never read.
+//   * Host threads: the per-device address is kept in an atomic slot, so first calls made at the same time from
+//     several host threads are safe (each may do the look-up; all store the same address). The error message of a
+//     failed call is kept per host thread.
 //   * It calls no cudaMalloc, cudaFree or allocating library routine, torch's included. Results equal slb_argmax's:
 //     the index of the largest of logits[r, 0 .. limit), the lowest index on ties.
 // Returns 0, or a non-zero code with the message available from slb_last_error().

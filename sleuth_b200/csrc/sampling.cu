@@ -22,6 +22,8 @@
 
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "no_alloc.h"
 
@@ -598,6 +600,7 @@ extern "C" long long slb_argmax_scratch_words(int rows) { return 2ll * rows * kA
 extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit, int* out, void* scratch,
                           long long scratch_words, void* stream) {
   SLB_REQUIRE(rows >= 0 && rows < 65536 && limit > 0 && ld >= limit, "argmax: rows=%d limit=%d ld=%lld", rows, limit, ld);
+  SLB_REQUIRE(rows == 0 || (logits != nullptr && out != nullptr), "argmax: logits and out must be device pointers, not null");
   SLB_REQUIRE(scratch != nullptr && scratch_words >= slb_argmax_scratch_words(rows),
               "argmax: %lld words of scratch memory are needed, %lld were given", slb_argmax_scratch_words(rows), scratch_words);
   if (rows == 0) return 0;
@@ -617,10 +620,11 @@ extern "C" int slb_argmax(const float* logits, long long ld, int rows, int limit
 // for once per device (cudaGetSymbolAddress, with that device current) and kept.
 constexpr int kStaticArgmaxRows = SLB_ARGMAX_STATIC_MAX_ROWS;
 static __device__ __align__(256) unsigned int g_argmax_scratch[2 * kStaticArgmaxRows * kArgmaxChunks];
-static void* g_argmax_scratch_addr[64] = {nullptr};
+static std::atomic<void*> g_argmax_scratch_addr[64];     // per device; host threads may race to fill a slot: all write the same address
 
 extern "C" int slb_argmax_static(const float* logits, long long ld, int rows, int limit, int* out, void* stream) {
   SLB_REQUIRE(rows >= 0 && limit > 0 && ld >= limit, "argmax_static: rows=%d limit=%d ld=%lld", rows, limit, ld);
+  SLB_REQUIRE(rows == 0 || (logits != nullptr && out != nullptr), "argmax_static: logits and out must be device pointers, not null");
   SLB_REQUIRE(rows <= kStaticArgmaxRows,
               "argmax_static: %d rows are more than the built-in scratch array holds (%d); use slb_argmax with scratch "
               "memory of your own", rows, kStaticArgmaxRows);
@@ -628,15 +632,15 @@ extern "C" int slb_argmax_static(const float* logits, long long ld, int rows, in
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(2, "argmax_static: no usable current device (%s)", cudaGetErrorString(e));
-  if (g_argmax_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_argmax_scratch);     // first call on this device; not during stream capture
-    if (e != cudaSuccess || p == nullptr)
+  void* base = g_argmax_scratch_addr[dev].load(std::memory_order_acquire);
+  if (base == nullptr) {
+    e = cudaGetSymbolAddress(&base, g_argmax_scratch);     // first call on this device; not during stream capture
+    if (e != cudaSuccess || base == nullptr)
       return fail(2, "argmax_static: cannot find the scratch array on device %d: %s", dev, cudaGetErrorString(e));
-    g_argmax_scratch_addr[dev] = p;
+    g_argmax_scratch_addr[dev].store(base, std::memory_order_release);
   }
-  float* part_v = (float*)g_argmax_scratch_addr[dev];
-  int* part_i = (int*)g_argmax_scratch_addr[dev] + (size_t)kStaticArgmaxRows * kArgmaxChunks;
+  float* part_v = (float*)base;
+  int* part_i = (int*)base + (size_t)kStaticArgmaxRows * kArgmaxChunks;
   cudaStream_t s = (cudaStream_t)stream;
   // every slot that the second stage reads is written by the first stage of the same call, so nothing left in
   // the array by an earlier call is ever read and nothing has to be cleared

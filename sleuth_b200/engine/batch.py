@@ -72,9 +72,17 @@ class MetaStager:
         self._grow(capacity)
 
     def _grow(self, capacity: int) -> None:
+        """Replace the buffers by larger ones. The token feed at the start of the device buffer is carried over:
+        in the pipelined loop the sampler has already left the next step's tokens there when an upload finds the
+        buffer too small. Views of the old buffer that a caller still holds (``feed``) go stale; ``generation``
+        tells (the stepper drops its recorded graphs on it, and ``Stepper.feed`` is looked up afresh each time)."""
         torch.cuda.synchronize(self.device)
+        old = self.dev
         self.cap = capacity
         self.dev = torch.zeros(capacity, dtype=torch.int32, device=self.device)
+        if old is not None:
+            self.dev[:self.FEED].copy_(old[:self.FEED])
+            torch.cuda.synchronize(self.device)
         self.hosts = [torch.zeros(capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.events = [None] * self.RING
         self.generation += 1

@@ -61,6 +61,8 @@ class Stepper:
         self._decode_logits: torch.Tensor | None = None
         self._graph_key = None
         self.check_kernels = os.environ.get("SLEUTH_B200_CHECK", "0") == "1"   # read the kernels' status word after each step
+        self._status_host: torch.Tensor | None = None     # pinned copy of the kernels' status word, read one step late
+        self._status_event = None
         self._graph_own: dict = {}          # own kernel launches captured in each graph
         self.graph_kernel_launches = 0      # own kernel launches replayed through graphs so far
         ops.lib()   # build or load the kernels now; fail here, loudly, if that is impossible
@@ -72,6 +74,7 @@ class Stepper:
         buffer that the next step overwrites."""
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
+        self._raise_late_status()
         toks = [np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries]
         book = self.cache.book
         for e, t in zip(entries, toks):
@@ -93,13 +96,39 @@ class Stepper:
         if all(t.size == 1 for t in toks):
             return self._decode(entries, slots, toks, floats)
 
+        chunks = self._cut(toks)
+        # All or nothing: a step that the cache cannot hold to its end is refused before its first chunk runs, so a
+        # sequence is never left half-appended.
+        lens = {s: int(book.lengths[s]) for s in slots}
+        plan = []
+        for chunk in chunks:
+            c_slots = [slots[i] for i, _, _ in chunk]
+            for (i, _, take), s in zip(chunk, c_slots):
+                lens[s] += take
+            plan.append((c_slots, [lens[s] for s in c_slots]))
+        for g, need in zip(book.groups, book.peak_pages_needed(plan)):
+            if need > g.pool.free:
+                raise CacheFull(f"the step needs {need} more pages of 64 tokens and {g.pool.free} of {g.pool.n_pages} "
+                                f"are free; nothing of it was run")
+
         n_want = sum(len(e.want) for e in entries)
         out = torch.empty((n_want, self.model.vocab), dtype=torch.float32, device=self.device)
         out_base, acc = [], 0
         for e in entries:
             out_base.append(acc)
             acc += len(e.want)
-        done = [0] * len(entries)
+        for chunk in chunks:
+            self._run_chunk(entries, slots, toks, chunk, out, out_base)
+        if self.check_kernels:
+            ops.gemm_tc_check(self.device)
+        else:
+            self._status_later()
+        return out
+
+    def _cut(self, toks) -> list:
+        """The chunks of a step: lists of (entry index, first token, tokens) with at most ``max_step_tokens`` tokens
+        each, entries in order, an entry that does not fit going on in the next chunk."""
+        chunks, done = [], [0] * len(toks)
         while True:
             chunk, room = [], self.max_step_tokens
             for i, t in enumerate(toks):
@@ -109,13 +138,40 @@ class Stepper:
                     chunk.append((i, done[i], take))
                     room -= take
             if not chunk:
-                break
-            self._run_chunk(entries, slots, toks, chunk, out, out_base)
+                return chunks
+            chunks.append(chunk)
             for i, start, take in chunk:
                 done[i] = start + take
-        if self.check_kernels:
-            ops.gemm_tc_check(self.device)
-        return out
+
+    # ------------------------------------------------------------ the kernels' status word ----
+    def _status_later(self) -> None:
+        """After a step of many tokens (the tcgen05 kernels serve those): start a copy of the kernels' status word
+        to pinned memory. It is looked at when the next step begins, without waiting for the device, and at
+        ``check_status``; a bounded wait that gave up inside a kernel is then reported one step late instead of never."""
+        status = ops.tc_status(self.device)
+        if status is None:
+            return
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        elif self._status_event is not None and not self._status_event.query():
+            return                      # the earlier copy has not landed yet; it will tell the same story
+        self._status_host.copy_(status, non_blocking=True)
+        self._status_event = torch.cuda.Event()
+        self._status_event.record()
+
+    def _raise_late_status(self, wait: bool = False) -> None:
+        ev = self._status_event
+        if ev is None or not (wait or ev.query()):
+            return
+        ev.synchronize()
+        self._status_event = None
+        if int(self._status_host[0]):
+            ops.gemm_tc_check(self.device)          # reads the word itself, clears it and raises
+
+    def check_status(self) -> None:
+        """Raise if a kernel's bounded wait gave up in any step so far (waits for the device)."""
+        self._raise_late_status(wait=True)
+        ops.gemm_tc_check(self.device)
 
     # ------------------------------------------------------------------ chunks ----
     def _run_chunk(self, entries, slots, toks, chunk, out, out_base) -> None:
@@ -215,6 +271,7 @@ class Stepper:
         """One token for each of ``slots``, taken from the device-side feed: sequence i reads
         ``feed[feed_map[i]]``, where the sampler left the tokens it chose for the previous step's rows.
         Returns the logits of every row (a view that the next step overwrites)."""
+        self._raise_late_status()
         book = self.cache.book
         slots = [int(s) for s in slots]
         if len(slots) > self.meta.FEED:

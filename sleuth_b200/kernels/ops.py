@@ -129,18 +129,36 @@ def flash_supported(head_dim: int, dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128)
 
 
-def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> int:
+_SMS: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device, asked of the library once (148 on a B200). The launch choices made
+    in Python count with the same number as those made in the launchers."""
+    key = torch.cuda.current_device() if device is None else torch.device(device).index
+    if key not in _SMS:
+        fn = lib().dll.slb_sm_count
+        fn.restype = ctypes.c_int
+        with torch.cuda.device(key):
+            _SMS[key] = int(fn())
+    return _SMS[key]
+
+
+def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int, sms: int | None = None) -> int:
     """Slices of the key range per (sequence, kv head) in a decode step: enough blocks to fill the
     GPU a few times over, never more than a sequence can have pages. It depends on the batch size
-    only, not on the lengths, so a captured step stays valid as sequences grow."""
+    only, not on the lengths, so a captured step stays valid as sequences grow. ``sms``: the device's
+    multiprocessors (asked of the library when not given)."""
+    if sms is None:
+        sms = sm_count()
     blocks = max(1, n_seqs * kv_heads * ((group + 15) // 16))
     # Two blocks of this kernel fit an SM with its three page buffers (100 KB of shared memory at head size 128),
-    # three with two buffers, which the launcher picks when that makes all blocks run at once: 148 * 2 or 148 * 3.
+    # three with two buffers, which the launcher picks when that makes all blocks run at once: 2 or 3 per SM.
     # All slices should run in one wave.
-    resident = 148 * 2
+    resident = sms * 2
     if blocks >= resident:
         return 1
-    if 2 * blocks > resident and 2 * blocks <= 148 * 3 and table_stride >= 8:
+    if 2 * blocks > resident and 2 * blocks <= sms * 3 and table_stride >= 8:
         return 2          # one slice each would leave half the GPU idle; two fit with two page buffers
     # merging the slices costs a few microseconds that grow with their number: a slice should hold at least
     # four pages of the longest sequence
@@ -148,7 +166,7 @@ def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int) -> 
     three_buffers = max(1, min(resident // blocks, 64, most))
     # with two page buffers three blocks fit an SM: more, shorter slices in the same single round (measured at
     # batch 8: 18.7 us with 6 slices against 19.5 us with 4 at 2,112 keys; 7 slices, a second round, take 24.2 us)
-    two_buffers = max(1, min((148 * 3) // blocks, 64, most))
+    two_buffers = max(1, min((sms * 3) // blocks, 64, most))
     # only where that is half as many slices again: batch 8, 6 for 4 slices, 0.982 against 1.010 ms a step; batch 16,
     # 3 for 2, 1.395 against 1.412 ms; batch 12, 4 for 3, is slower, 1.197 against 1.171 ms
     if 2 * two_buffers >= 3 * three_buffers and two_buffers * blocks > resident:
@@ -393,6 +411,11 @@ def gemm_tc_qkv(x, w, heads: int, kv_heads: int, head_dim: int, bias, q_gain, k_
                _p(sin), float(eps), _p(q_out), _p(k_pool) if kv_heads else None, _p(v_pool) if kv_heads else None,
                _p(tok_seq), _p(tok_pos), _p(block_table), 0 if block_table is None else block_table.shape[1],
                _p(_tc_status(x.device)), stream if stream is not None else current_stream())
+
+
+def tc_status(device):
+    """The status word of the tcgen05 kernels on ``device`` (an int32 CUDA tensor), or None if none has run there."""
+    return _TC_STATUS.get(str(torch.device(device)))
 
 
 def gemm_tc_check(device) -> None:

@@ -15,7 +15,7 @@ def test_decode_slices_fill_one_round_and_never_more(kv_heads, group, table_stri
     row_tiles = (group + 15) // 16
     for n in list(range(1, 70)) + [100, 300]:
         blocks = n * kv_heads * row_tiles
-        s = ops.decode_splits(n, kv_heads, group, table_stride)
+        s = ops.decode_splits(n, kv_heads, group, table_stride, sms=148)
         assert s >= 1
         # a slice holds at least four pages of the longest sequence, unless one slice per pair is all there is
         assert s == 1 or s <= max(1, table_stride // 4) or s == 2
@@ -25,16 +25,16 @@ def test_decode_slices_fill_one_round_and_never_more(kv_heads, group, table_stri
         else:
             assert s == 1 or s * blocks <= 3 * SMS
         # it depends on the batch and the table's width only: the same answer again
-        assert s == ops.decode_splits(n, kv_heads, group, table_stride)
+        assert s == ops.decode_splits(n, kv_heads, group, table_stride, sms=148)
 
 
 def test_decode_slices_at_the_benchmark_shapes():
     # 8 kv heads, 2 query heads each, sequences of up to 4,096 keys (64 pages)
-    assert ops.decode_splits(1, 8, 2, 64) == 16      # capped: four pages a slice
-    assert ops.decode_splits(8, 8, 2, 64) == 6       # 384 blocks with two page buffers, not 256 with three
-    assert ops.decode_splits(12, 8, 2, 64) == 3      # 4 for 3 would not pay
-    assert ops.decode_splits(16, 8, 2, 64) == 3
-    assert ops.decode_splits(64, 8, 2, 64) == 1
+    assert ops.decode_splits(1, 8, 2, 64, sms=148) == 16      # capped: four pages a slice
+    assert ops.decode_splits(8, 8, 2, 64, sms=148) == 6       # 384 blocks with two page buffers, not 256 with three
+    assert ops.decode_splits(12, 8, 2, 64, sms=148) == 3      # 4 for 3 would not pay
+    assert ops.decode_splits(16, 8, 2, 64, sms=148) == 3
+    assert ops.decode_splits(64, 8, 2, 64, sms=148) == 1
 
 
 def test_norm_is_fused_only_where_it_was_measured_to_pay():
