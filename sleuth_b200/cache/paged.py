@@ -6,8 +6,9 @@ Each layer application has one cache *entry*. A part asks for what its entry nee
   ``window`` positions). Entries with equal requests form a *group*; a group owns one tensor
   ``[entries, 2, pages, kv_heads, 64, head_dim]`` (index 1: 0 = keys, 1 = values), so a page number
   means the same place in every entry of the group and one block table serves them all.
-* ``StateRequest(shape, dtype)``: a fixed-size state per sequence, ``[max_slots, *shape]``, zeroed
-  when a slot is taken. The Qwen3 decoder has none; a recurrent or convolutional mixer would keep
+* ``StateRequest(shape, dtype)``: a fixed-size state per sequence, ``[max_sequences, *shape]``, zeroed
+  when a slot is taken. It is sized by the number of sequences that may be live at once, not by the
+  number of pages: a state of a megabyte per sequence beside a cache of thousands of pages stays small. The Qwen3 decoder has none; a recurrent or convolutional mixer would keep
   its state here (the reference keeps such state beside the keys and values of the same batch row,
   sleuth/formats/qwen35.py:132-145, and a per-row token history, sleuth/forge/infer/kv_cache.py:37-43).
 * ``None``: the entry holds nothing.
@@ -57,14 +58,25 @@ class StateView:
 class PagedCache:
     """Pools and state regions for a list of requests (one per cache entry), plus the bookkeeping."""
 
+    # Sequences live at once when the caller names no number and some entry keeps per-sequence state.
+    DEFAULT_SEQUENCES_WITH_STATE = 256
+
     def __init__(self, requests: list, max_tokens: int, max_seq_len: int, dtype: torch.dtype, device,
-                 max_slots: int | None = None):
+                 max_sequences: int | None = None):
+        """max_tokens: tokens all live sequences may hold together (pages of 64). max_sequences: how many
+        sequences may be live at once (slots). Default: one per page, the most that can ever hold a token, unless
+        some entry keeps a per-sequence state, which is allocated for every slot: then 256 at most."""
         self.dtype = dtype
         self.device = torch.device(device)
         self.n_pages = max(1, pages_for(max_tokens))
         self.stride = max(1, pages_for(max_seq_len))
-        self.max_slots = max_slots if max_slots is not None else self.n_pages
         self.requests = list(requests)
+        if max_sequences is None:
+            has_state = any(isinstance(r, StateRequest) for r in self.requests)
+            max_sequences = min(self.n_pages, self.DEFAULT_SEQUENCES_WITH_STATE) if has_state else self.n_pages
+        if max_sequences < 1:
+            raise ValueError(f"max_sequences must be at least 1, got {max_sequences}")
+        self.max_slots = int(max_sequences)
 
         keys: list[KVRequest] = []
         self.entry_group: list[int | None] = []

@@ -407,6 +407,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
 }
 
+// What every tensor-memory kernel here does when one of its waits runs out, as a kernel of its own, so that the
+// path can be exercised without anything going wrong: the block takes tensor memory, one thread waits `polls` times
+// on a barrier that nothing will ever complete, records `code` in the status word, and the block gives its tensor
+// memory back and returns. Nothing faults and nothing hangs; the host then finds the code.
+__global__ void __launch_bounds__(64) tc_wait_probe_kernel(int* status, uint32_t polls, int code) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_addr(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(32) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0 && !mbar_wait(smem_addr(&bar), 0, polls)) atomicExch(status, code);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32) : "memory");
+}
+
 // ------------------------------------------------------------------------------------ host side ----
 // A [rows, K] bfloat16 row-major matrix seen through boxes of box_rows x 64 elements, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
@@ -444,6 +471,15 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs&
 }  // namespace slb
 
 using namespace slb;
+
+// Runs the give-up path of the tensor-memory kernels on purpose, harmlessly (see tc_wait_probe_kernel): after it,
+// `status` holds `code`. polls: how often the one waiting thread looks at its barrier (1 to 1,000,000).
+extern "C" int slb_tc_wait_probe(int* status, int polls, int code, void* stream) {
+  SLB_REQUIRE(status != nullptr && polls >= 1 && polls <= 1000000 && code != 0, "tc_wait_probe: status=%p polls=%d code=%d",
+              (void*)status, polls, code);
+  launch(tc_wait_probe_kernel, dim3(1), dim3(64), 0, (cudaStream_t)stream, status, (uint32_t)polls, code);
+  return check_launch("tc_wait_probe");
+}
 
 extern "C" int slb_gemm_tc_supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
 

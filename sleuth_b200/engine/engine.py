@@ -65,13 +65,15 @@ class Engine:
     # ------------------------------------------------------------------ loading ----
     @classmethod
     def from_pretrained(cls, folder, dtype="bf16", max_seq_len: int = 4096, max_tokens: int | None = None,
-                        device="cuda:0", use_graphs: bool = True, max_step_tokens: int = 8192) -> "Engine":
+                        device="cuda:0", use_graphs: bool = True, max_step_tokens: int = 8192,
+                        max_sequences: int | None = None) -> "Engine":
         """Load ``folder`` (``config.json`` + safetensors).
 
         max_seq_len: the longest sequence (prompt plus new tokens); capped by the model's
         ``max_position_embeddings`` (sleuth/formats/hf.py:96). max_tokens: how many tokens all live
         sequences may hold together (each rounded up to 64); sizes the cache. Default: 8 sequences
-        of ``max_seq_len``."""
+        of ``max_seq_len``. max_sequences: how many sequences may be live at once (sizes the slot tables and
+        any per-sequence state; see ``PagedCache``)."""
         if not torch.cuda.is_available():
             raise RuntimeError("sleuth_b200 runs on an NVIDIA GPU only; torch.cuda.is_available() is False")
         run_dtype = resolve_dtype(dtype)
@@ -89,13 +91,13 @@ class Engine:
             del tensors
         if max_tokens is None:
             max_tokens = 8 * max_seq_len
-        cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device)
+        cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device, max_sequences)
         return cls(cfg, spec, model, cache, device, run_dtype, max_seq_len, unread, use_graphs, max_step_tokens)
 
     @classmethod
     def from_config(cls, config_json: dict, seed: int = 0, dtype="bf16", max_seq_len: int = 4096,
                     max_tokens: int | None = None, device="cuda:0", use_graphs: bool = True,
-                    max_step_tokens: int = 8192, std: float = 0.02) -> "Engine":
+                    max_step_tokens: int = 8192, std: float = 0.02, max_sequences: int | None = None) -> "Engine":
         """A model with random weights drawn on the device from a ``config.json`` dictionary and a
         seed: matrices and biases ~ N(0, std), norm gains ~ 1 + N(0, std). Nothing is written to disk
         (``weights.write_random_model`` writes a folder instead, with a generator that is the same on
@@ -125,7 +127,7 @@ class Engine:
         del tensors
         if max_tokens is None:
             max_tokens = 8 * max_seq_len
-        cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device)
+        cache = PagedCache(model.cache_requests, max_tokens, max_seq_len, run_dtype, device, max_sequences)
         return cls(cfg, spec, model, cache, device, run_dtype, max_seq_len, unread, use_graphs, max_step_tokens)
 
     # ------------------------------------------------------------------ stepping ----
@@ -190,6 +192,7 @@ class Engine:
             stop_ids = set(getattr(self.config, "stop_ids", ()))
         before = self.stepper.use_graphs
         self.stepper.use_graphs = before and cuda_graph
+        max_batch = max(1, min(int(max_batch), self.cache.max_slots))
         self.pipelined = len(prompts) <= self.stepper.feed.numel() and max_batch <= self.stepper.feed.numel()
         try:
             results = generate_batches(self, prompts, max_new_tokens, sampling, stop_ids, vocab_limit, seed, on_token,

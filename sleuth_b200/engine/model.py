@@ -16,21 +16,21 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import BuildContext, ParamDecl, build_layer, lead_weight_of
-from ..parts.ends import LMHead, TokenEmbedding
+from ..parts import ends as _ends   # noqa: F401  (registers the token embedding and the output head)
+from ..parts.base import BuildContext, ParamDecl, build_embedding, build_head, build_layer, lead_weight_of
 from ..parts.spec import ModelSpec
 
 
 class Model:
     def __init__(self, spec: ModelSpec, ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
-        self.embedding = TokenEmbedding(spec.embedding, ctx)
+        self.embedding = build_embedding(spec.embedding, ctx)      # by ``spec.kind``, like every other part
         self.layers = [build_layer(ls, ctx) for ls in spec.layers]
-        self.head = LMHead(spec.head, ctx)
+        self.head = build_head(spec.head, ctx)
         self.hidden = spec.embedding.dim
         self.vocab = spec.head.vocab
         # single-token steps are recorded as CUDA graphs only if every layer allows it
-        self.capturable = all(getattr(layer, "capturable", True) for layer in self.layers)
+        self.capturable = all(getattr(part, "capturable", True) for part in (self.embedding, *self.layers, self.head))
         # cache entries: the first application that names an entry owns it
         self.entry_owner: dict[int, int] = {}
         for i, e in enumerate(spec.schedule):
@@ -39,27 +39,43 @@ class Model:
                                for c in range(len(self.entry_owner))]
 
     # ---- weights ----
+    def _end_names(self, which: str) -> dict[str, str]:
+        """Checkpoint names of the tensors an end part declares: ``weight`` (and the head's ``norm.weight``) from the
+        spec's own fields, anything else from the spec's ``names``."""
+        spec = getattr(self.spec, which)
+        part = getattr(self, which)
+        given = dict(getattr(spec, "names", {}) or {})
+        given.setdefault("weight", spec.name)
+        if which == "head":
+            given.setdefault("norm.weight", spec.norm_name)
+        out = {}
+        for local in part.declare():
+            if local not in given:
+                raise KeyError(f"{which}: its description gives no checkpoint name for tensor {local!r}")
+            out[local] = given[local]
+        return out
+
     def expected(self) -> dict[str, ParamDecl]:
-        out = {self.spec.embedding.name: self.embedding.declare()["weight"]}
+        out = {}
+        emb = self.embedding.declare()
+        for local, name in self._end_names("embedding").items():
+            out[name] = emb[local]
         for i, (layer, ls) in enumerate(zip(self.layers, self.spec.layers)):
             for local, decl in layer.declare().items():
                 if local not in ls.names:
                     raise KeyError(f"layer {i}: its description gives no checkpoint name for tensor {local!r}")
                 out[ls.names[local]] = decl
         hd = self.head.declare()
-        out[self.spec.head.norm_name] = hd["norm.weight"]
-        if "weight" in hd:
-            out[self.spec.head.name] = hd["weight"]
+        for local, name in self._end_names("head").items():
+            out[name] = hd[local]
         return out
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.embedding.bind({"weight": tensors[self.spec.embedding.name]})
+        self.embedding.bind({local: tensors[name] for local, name in self._end_names("embedding").items() if name in tensors})
         for layer, ls in zip(self.layers, self.spec.layers):
             layer.bind({local: tensors[ls.names[local]] for local in layer.declare() if ls.names[local] in tensors})
-        head = {"norm.weight": tensors[self.spec.head.norm_name]}
-        if not self.spec.head.tied:
-            head["weight"] = tensors[self.spec.head.name]
-        self.head.bind(head, embedding_table=self.embedding.table)
+        head = {local: tensors[name] for local, name in self._end_names("head").items() if name in tensors}
+        self.head.bind(head, embedding_table=getattr(self.embedding, "table", None))
 
     # ---- one step ----
     def forward(self, b, cache, ws, logits: torch.Tensor) -> torch.Tensor:
@@ -67,7 +83,7 @@ class Model:
         b.stream = torch.cuda.current_stream().cuda_stream   # inside a graph capture this is the capture stream
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
-        self.embedding.forward(b.token_ids, x, b.stream, b.ids_map)
+        self.embedding.forward(b, x)
         schedule = self.spec.schedule
         for i, e in enumerate(schedule):
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
@@ -76,7 +92,7 @@ class Model:
             self.layers[e.layer].forward(x, b, view, ws)
         b.next_read = None
         if logits.shape[0]:
-            self.head.forward(x, b.rows, logits, ws, b.stream)
+            self.head.forward(x, b, logits, ws)
         ws.release(mark)
         return logits
 
@@ -89,16 +105,17 @@ class Model:
         return total
 
     def _all_tensors(self):
-        yield self.embedding.table
-        yield self.head.proj.weight
-        yield self.head.norm.weight
+        """The tensors the parts hold: attributes that are tensors, or objects with a tensor ``weight`` (a product,
+        a norm), looked for in the end parts and in each layer's ``children``."""
+        parts = [self.embedding, self.head]
         for layer in self.layers:
-            for part in getattr(layer, "children", {}).values():
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        yield v
-                    elif hasattr(v, "weight") and isinstance(getattr(v, "weight"), torch.Tensor):
-                        yield v.weight
+            parts.extend(getattr(layer, "children", {}).values())
+        for part in parts:
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    yield v
+                elif isinstance(getattr(v, "weight", None), torch.Tensor):
+                    yield v.weight
 
 
 def declare_model(spec: ModelSpec) -> dict[str, ParamDecl]:

@@ -413,6 +413,15 @@ def gemm_tc_qkv(x, w, heads: int, kv_heads: int, head_dim: int, bias, q_gain, k_
                _p(_tc_status(x.device)), stream if stream is not None else current_stream())
 
 
+def tc_wait_probe(device, polls: int = 1000, code: int = 99, stream=None) -> None:
+    """Run the give-up path of the tensor-memory kernels on purpose and harmlessly: a one-block kernel takes tensor
+    memory, waits ``polls`` times on a barrier that nothing completes, records ``code`` in the status word, frees its
+    tensor memory and returns. ``gemm_tc_check`` then raises. For tests of that path; nothing faults or hangs."""
+    with torch.cuda.device(torch.device(device)):
+        lib().call("slb_tc_wait_probe", _p(_tc_status(torch.device(device))), int(polls), int(code),
+                   stream if stream is not None else current_stream())
+
+
 def tc_status(device):
     """The status word of the tcgen05 kernels on ``device`` (an int32 CUDA tensor), or None if none has run there."""
     return _TC_STATUS.get(str(torch.device(device)))
@@ -428,7 +437,8 @@ def gemm_tc_check(device) -> None:
         st.zero_()
         raise RuntimeError(f"a wait inside a tcgen05 kernel gave up (code {code}; product: 1 = free stage, 2 = loaded "
                            f"stage, 3 = finished accumulator, 4 = drained accumulator; attention: 20 = shared memory "
-                           f"misaligned, 21-27 = producer and MMA waits, 28-32 = softmax waits); its results are not valid")
+                           f"misaligned, 21-27 = producer and MMA waits, 28-32 = softmax waits; 99 = the wait probe of the tests); "
+                           f"its results are not valid")
 
 
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:

@@ -17,8 +17,11 @@ is float32 ``[tokens, hidden]``; ``h`` is in the run dtype):
 * ffn:       ``forward(h, x, b, ws)``                          adds its output into ``x`` in place
              (a mixer or ffn with ``accepts_normed = True`` gets a ``Normed`` for ``h``, see below)
 * layer:     ``forward(x, b, view, ws)``                       one whole layer on the stream, in place
-* embedding: ``forward(ids, x)``                               fills ``x`` from token ids
-* head:      ``forward(x, rows, logits, ws)``                  final norm + output matrix on chosen rows
+* embedding: ``forward(b, x)``                                 fills ``x`` from the batch's token ids (and, if it
+                                                               wants, their positions ``b.tok_pos``); a part whose
+                                                               table a tied head may use exposes it as ``table``
+* head:      ``forward(x, b, logits, ws)``                     final norm + output matrix on the rows ``b.rows``;
+                                                               ``bind(tensors, embedding_table=...)``
 
 Roles decide the dtype a tensor is kept in on the device: ``"matrix"`` in the run dtype (bfloat16
 on the fast path), ``"vector"`` (gains, biases) in float32, ``"table"`` (integer tables) in int32.
@@ -29,7 +32,8 @@ A part whose ``forward`` must run afresh every step (it reads the step's host-si
 depend on the data) sets ``capturable = False``; single-token steps are then not recorded as CUDA graphs.
 
 New kinds are added with ``register_norm``, ``register_position``, ``register_mixer``,
-``register_ffn``, ``register_layer``; a spec's ``kind`` selects the class.
+``register_ffn``, ``register_layer``, ``register_embedding``, ``register_head``; a spec's ``kind``
+selects the class.
 """
 
 from __future__ import annotations
@@ -104,7 +108,8 @@ def lead_weight_of(part):
     return f() if callable(f) else None
 
 
-_REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "layer": {}}
+_REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "layer": {},
+                                           "embedding": {}, "head": {}}
 
 
 def _register(family: str, kind: str, cls: type) -> None:
@@ -125,6 +130,8 @@ def register_position(kind, cls): _register("position", kind, cls)
 def register_mixer(kind, cls): _register("mixer", kind, cls)
 def register_ffn(kind, cls): _register("ffn", kind, cls)
 def register_layer(kind, cls): _register("layer", kind, cls)
+def register_embedding(kind, cls): _register("embedding", kind, cls)
+def register_head(kind, cls): _register("head", kind, cls)
 
 
 def build_norm(spec, ctx): return _build("norm", spec, ctx)
@@ -137,6 +144,8 @@ def build_position(spec, ctx):
 def build_mixer(spec, ctx): return _build("mixer", spec, ctx)
 def build_ffn(spec, ctx): return _build("ffn", spec, ctx)
 def build_layer(spec, ctx): return _build("layer", spec, ctx)
+def build_embedding(spec, ctx): return _build("embedding", spec, ctx)
+def build_head(spec, ctx): return _build("head", spec, ctx)
 
 
 def unregister(family: str, kind: str) -> None:

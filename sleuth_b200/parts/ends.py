@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, ParamDecl, Part, build_norm
+from .base import BuildContext, ParamDecl, Part, build_norm, register_embedding, register_head
 from .linear import Linear
 from .spec import EmbeddingSpec, HeadSpec
 
@@ -23,8 +23,10 @@ class TokenEmbedding(Part):
     def bind(self, t):
         self.table = t["weight"]
 
-    def forward(self, ids, x, stream=None, ids_map=None):
-        ops.embed(ids, self.table, x, self.spec.scale, stream, ids_map)
+    def forward(self, b, x):
+        """``b``: the step's batch; its token ids sit in ``b.token_ids`` (read through ``b.ids_map`` in a step that
+        takes its tokens from the device-side feed)."""
+        ops.embed(b.token_ids, self.table, x, self.spec.scale, b.stream, b.ids_map)
 
 
 class LMHead(Part):
@@ -47,10 +49,14 @@ class LMHead(Part):
         w = embedding_table if self.spec.tied else t["weight"]
         self.proj = Linear(w, self.ctx.dtype)
 
-    def forward(self, x, rows, logits, ws, stream=None):
-        """logits[r] = head(x[rows[r]]); ``logits`` is float32 [len(rows), vocab]."""
+    def forward(self, x, b, logits, ws):
+        """logits[r] = head(x[b.rows[r]]); ``logits`` is float32 [len(b.rows), vocab]."""
         mark = ws.mark()
         h = ws.take((logits.shape[0], self.spec.dim), self.ctx.dtype)
-        self.norm.forward(x, h, rows, stream)
-        self.proj.forward(h, out=logits, stream=stream)
+        self.norm.forward(x, h, b.rows, b.stream)
+        self.proj.forward(h, out=logits, stream=b.stream)
         ws.release(mark)
+
+
+register_embedding("token_embedding", TokenEmbedding)
+register_head("lm_head", LMHead)

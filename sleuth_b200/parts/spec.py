@@ -85,6 +85,9 @@ class ScheduleEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """The part that fills the stream from token ids. ``name`` is the checkpoint name of its tensor ``weight``; a
+    part of another ``kind`` that declares more tensors gives their checkpoint names in a field ``names``
+    (local name -> checkpoint name) of its own spec class."""
     vocab: int
     dim: int
     scale: float = 1.0
@@ -94,7 +97,9 @@ class EmbeddingSpec:
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """Final norm and output matrix. ``tied``: the output matrix is the embedding table."""
+    """Final norm and output matrix. ``tied``: the output matrix is the embedding table. ``norm_name`` and ``name``
+    are the checkpoint names of the tensors ``norm.weight`` and ``weight``; more tensors of another ``kind`` are
+    named by a field ``names`` (local name -> checkpoint name) of its own spec class."""
     vocab: int
     dim: int
     norm: NormSpec

@@ -40,3 +40,9 @@ def model_folders(tmp_path_factory):
         write_random_model(d, cfg, seed=tiny.SEEDS[name], dtype=torch.float32)
         out[name] = str(d)
     return out
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest differences from the plain implementation that the GPU tests saw (tests/closeness.py)."""
+    import closeness
+    closeness.report(terminalreporter.write_line)

@@ -161,13 +161,14 @@ def block(x: torch.Tensor, w: dict[str, torch.Tensor], i: int, s: dict, cos, sin
 
 
 def logits(cfg: dict, w: dict[str, torch.Tensor], tokens, work: torch.dtype = torch.float32,
-           round_weights_to_bf16: bool = False) -> torch.Tensor:
+           round_weights_to_bf16: bool = False, rows=None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence: embedding lookup without scaling
     (sleuth/forge/model/transformer.py:345-348), the blocks, the final norm and the output
     matrix, which is the embedding when tied (:122,129-130,301-302).
 
     round_weights_to_bf16: every matrix and vector is first rounded to bfloat16 (what a
-    bfloat16 engine holds), the arithmetic stays in ``work``.
+    bfloat16 engine holds), the arithmetic stays in ``work``. rows: the positions whose logits are
+    returned (all of them when None); a large vocabulary makes the others expensive.
     """
     s = settings(cfg)
     if round_weights_to_bf16:
@@ -178,6 +179,8 @@ def logits(cfg: dict, w: dict[str, torch.Tensor], tokens, work: torch.dtype = to
     cos, sin = rope_tables(s["head_dim"], len(ids), s["theta"])
     for i in range(s["layers"]):
         x = block(x, w, i, s, cos, sin)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     h = rms_norm(x, w["model.norm.weight"], s["eps"])
     out = w["model.embed_tokens.weight"] if (s["tied"] or "lm_head.weight" not in w) else w["lm_head.weight"]
     return h @ out.T
@@ -241,7 +244,7 @@ def greedy_generate(cfg: dict, w: dict[str, torch.Tensor], prompt: list[int], ma
     ids = list(prompt)
     new = []
     for _ in range(max_new_tokens):
-        row = logits(cfg, w, ids, work)[-1]
+        row = logits(cfg, w, ids, work, rows=[len(ids) - 1])[0]
         tok = int(row.argmax())
         new.append(tok)
         ids.append(tok)

@@ -1,0 +1,133 @@
+"""The engine against the plain implementation at the benchmark's own layer sizes: hidden 1,024, 16 query and 8
+key/value heads of 128, intermediate 3,072, vocabulary 151,936, tied output matrix (the Qwen3-0.6B shape), with
+LAYERS = 3 of that model's 28 layers. Fewer layers is no smaller configuration: every kernel runs at the sizes
+and launch shapes that the benchmark times (the fused q/k/v epilogue with 24 heads a token, tcgen05 attention
+tiles, six-slice two-buffer decode attention at batch 8 behind the norm-fused few-rows product, the 4,748-block
+output product, all of it also inside replayed graphs). Schedules: each request alone and whole; a prefix and the
+last 32 tokens one by one; two unequal batches of eight through a cache with room for one; greedy generation
+through the entry point. In the manner of the reference's cache test (tests/test_model.py:61-69: chunked and
+token by token against the full forward)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from closeness import check
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+LAYERS = 3
+CONFIG = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=1024,
+              intermediate_size=3072, num_hidden_layers=LAYERS, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+              rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False, tie_word_embeddings=True,
+              max_position_embeddings=4096)
+SEED = 606
+
+# float32: summation order only (the same bound as for the tiny models). bfloat16: weights rounded alike on both
+# sides, activations and cache entries rounded in the engine only.
+TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=4e-2, atol=4e-2)}
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    from sleuth_b200.weights.random_init import write_random_model
+    d = tmp_path_factory.mktemp("model_06b_layers")
+    write_random_model(d, CONFIG, seed=SEED, dtype=torch.float32)
+    return str(d)
+
+
+@pytest.fixture(scope="module")
+def oracles(folder):
+    cfg, w = plain.read_model(folder)
+    w16 = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    cache = {}
+
+    def ref(dtype, ids, rows):
+        key = (dtype, tuple(ids), tuple(rows))
+        if key not in cache:
+            cache[key] = plain.logits(cfg, w16 if dtype == "bf16" else w, list(ids), rows=list(rows))
+        return cache[key]
+    return cfg, w, ref
+
+
+def requests(lengths, seed):
+    rng = np.random.default_rng(SEED + seed)
+    return [rng.integers(0, CONFIG["vocab_size"], size=n).tolist() for n in lengths]
+
+
+def load(folder, dtype, **kw):
+    import sleuth_b200 as sb
+    return sb.load(folder, dtype=dtype, max_seq_len=4096, **kw)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_each_request_alone_and_whole(dtype, folder, oracles):
+    _, _, ref = oracles
+    eng = load(folder, dtype, max_tokens=1024)
+    for ids in requests([5, 130, 300], seed=1):
+        rows = sorted(set(range(0, len(ids), 7)) | {len(ids) - 1, min(127, len(ids) - 1), min(128, len(ids) - 1)})
+        (slot,) = eng.open(1)
+        got = eng.step([(slot, ids, tuple(rows))]).cpu()
+        eng.close([slot])
+        check(got, ref(dtype, ids, rows), TOL[dtype], "benchmark shape " + dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_last_32_tokens_one_by_one(dtype, folder, oracles):
+    _, _, ref = oracles
+    eng = load(folder, dtype, max_tokens=1024)
+    for ids in requests([40, 300], seed=2):
+        cut = len(ids) - 32
+        (slot,) = eng.open(1)
+        rows = [eng.step([(slot, ids[:cut], (cut - 1,))]).cpu()]
+        for t in ids[cut:]:                      # the second single-token step onwards replays a recorded graph
+            rows.append(eng.step([(slot, [t], (0,))]).cpu().clone())
+        eng.close([slot])
+        check(torch.cat(rows), ref(dtype, ids, range(cut - 1, len(ids))), TOL[dtype], "benchmark shape " + dtype)
+    assert any(not isinstance(k[0], str) for k in eng.stepper._graphs)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_two_unequal_batches_of_eight_reuse_slots_and_pages(dtype, folder, oracles):
+    """Batch 8 is the benchmark's batch: in bfloat16 the decode attention then cuts every (sequence, kv head) into six
+    slices over two page buffers, behind the few-rows q/k/v product with the norm fused in. The cache has room for
+    one batch; the second gets the first one's slots and pages, still full of its keys. Shorter requests end earlier."""
+    _, _, ref = oracles
+    plans = [[(100, 6), (600, 9), (5, 9), (33, 1), (64, 4), (65, 9), (17, 2), (128, 5)],
+             [(1, 9), (130, 3), (63, 9), (450, 7), (12, 9), (200, 2), (90, 9), (64, 6)]]
+    pages = max(sum(-(-(p + d) // 64) for p, d in plan) for plan in plans)
+    eng = load(folder, dtype, max_tokens=64 * pages)
+    used = []
+    for b, plan in enumerate(plans):
+        reqs = requests([p + d for p, d in plan], seed=10 + b)
+        slots = eng.open(8)
+        used.append(set(slots))
+        got = {i: [] for i in range(8)}
+        out = eng.step([(s, ids[:p], (p - 1,)) for s, ids, (p, d) in zip(slots, reqs, plan)]).cpu()
+        for i in range(8):
+            got[i].append(out[i])
+        live, k = list(range(8)), 0
+        while live:
+            out = eng.step([(slots[i], [reqs[i][plan[i][0] + k]], (0,)) for i in live]).cpu()
+            for j, i in enumerate(live):
+                got[i].append(out[j].clone())
+            done = [i for i in live if k + 1 >= plan[i][1]]
+            eng.close([slots[i] for i in done])
+            live = [i for i in live if i not in done]
+            k += 1
+        for i, ids in enumerate(reqs):
+            p = plan[i][0]
+            check(torch.stack(got[i]), ref(dtype, ids, range(p - 1, len(ids))), TOL[dtype], "benchmark shape " + dtype)
+    assert used[0] == used[1] and eng.cache.book.pages_in_use() == [0]
+
+
+def test_greedy_generation_in_float32_equals_the_plain_loop(folder, oracles):
+    import sleuth_b200 as sb
+    cfg, w, _ = oracles
+    eng = load(folder, "fp32", max_tokens=2048)
+    prompts = requests([3, 40, 11], seed=20)
+    res = eng.generate(prompts, max_new_tokens=6, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())   # device-fed loop
+    assert [r.new_ids for r in res] == [plain.greedy_generate(cfg, w, p, 6) for p in prompts]

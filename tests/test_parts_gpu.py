@@ -130,8 +130,9 @@ def test_attention_part(dtype, hd, window, bias):
 
 def test_layer_embedding_and_head_parts():
     from sleuth_b200.cache.paged import PagedCache
-    from sleuth_b200.parts import Workspace, build_layer
-    from sleuth_b200.parts.ends import LMHead, TokenEmbedding
+    from types import SimpleNamespace
+
+    from sleuth_b200.parts import Workspace, build_embedding, build_head, build_layer
     from sleuth_b200.parts.spec import (AttentionSpec, EmbeddingSpec, GatedMLPSpec, HeadSpec, LayerSpec, NormSpec,
                                         PositionSpec)
     d, heads, kvh, hd, inter, eps, theta, vocab = 40, 4, 4, 10, 56, 1e-6, 1e4, 61
@@ -162,21 +163,25 @@ def test_layer_embedding_and_head_parts():
     cos, sin = plain.rope_tables(hd, 33, theta)
     torch.testing.assert_close(x.cpu(), plain.block(x0, pw, 0, s, cos, sin), rtol=1e-4, atol=1e-5)
 
-    emb = TokenEmbedding(EmbeddingSpec(vocab=vocab, dim=d, scale=2.0), c)
+    stream = torch.cuda.current_stream().cuda_stream
+    emb = build_embedding(EmbeddingSpec(vocab=vocab, dim=d, scale=2.0), c)       # by kind, as the model builds it
     table = torch.randn(vocab, d, generator=g)
     emb.bind({"weight": table.to(DEV)})
     ids = torch.tensor([0, 60, 7, 7], dtype=torch.int32)
     out = torch.empty(4, d, device=DEV)
-    emb.forward(ids.to(DEV), out)
+    emb.forward(SimpleNamespace(token_ids=ids.to(DEV), ids_map=None, stream=stream), out)
     torch.testing.assert_close(out.cpu(), table[ids.long()] * 2.0)
+    back = torch.tensor([3, 3, 0, 1], dtype=torch.int32)                          # through a device-side index map
+    emb.forward(SimpleNamespace(token_ids=ids.to(DEV), ids_map=back.to(DEV), stream=stream), out)
+    torch.testing.assert_close(out.cpu(), table[ids[back.long()].long()] * 2.0)
 
     for tied in (True, False):
-        head = LMHead(HeadSpec(vocab=vocab, dim=d, norm=NormSpec(d, eps), tied=tied), c)
+        head = build_head(HeadSpec(vocab=vocab, dim=d, norm=NormSpec(d, eps), tied=tied), c)
         assert ("weight" in head.declare()) == (not tied)
         gain, wout = 1 + 0.1 * torch.randn(d, generator=g), torch.randn(vocab, d, generator=g)
         head.bind({"norm.weight": gain.to(DEV), **({} if tied else {"weight": wout.to(DEV)})}, embedding_table=table.to(DEV))
         rows = torch.tensor([32, 0, 5], dtype=torch.int32, device=DEV)
         logits = torch.empty(3, vocab, device=DEV)
-        head.forward(x, rows, logits, Workspace(DEV))
+        head.forward(x, SimpleNamespace(rows=rows, stream=stream), logits, Workspace(DEV))
         ref = plain.rms_norm(x.cpu()[[32, 0, 5]], gain, eps) @ (table if tied else wout).T
         torch.testing.assert_close(logits.cpu(), ref, rtol=1e-4, atol=1e-4)

@@ -25,6 +25,7 @@ class ToyConfig:
     vocab_size: int
     hidden_size: int
     variant: str = "state"
+    head_dim: int = 16
     model_type: str = "toy"
 
 
@@ -52,12 +53,39 @@ class ScaledRotarySpec:
 
 
 EXPERTS, EXPERT_INNER, POS_FACTOR, ROT = 3, 40, 4.0, 8
+SOFTCAP, MAX_POS = 0.5, 256
+
+
+@dataclass(frozen=True)
+class LearnedPositionEmbeddingSpec:
+    """Token table plus a learned table of absolute positions: a position encoding that lives in the embedding."""
+    vocab: int
+    dim: int
+    positions: int
+    name: str = "model.embed_tokens.weight"
+    names: tuple = (("positions.weight", "model.embed_positions.weight"),)
+    kind: str = "learned_position_embedding"
+
+
+@dataclass(frozen=True)
+class SoftcapHeadSpec:
+    """Final norm, output matrix with a bias, logits squashed to (-cap, cap)."""
+    vocab: int
+    dim: int
+    norm: object
+    tied: bool
+    cap: float
+    norm_name: str = "model.norm.weight"
+    name: str = "lm_head.weight"
+    names: tuple = (("bias", "lm_head.bias"),)
+    kind: str = "softcap_head"
 
 
 def toy_spec(cfg: ToyConfig, tensor_names=None):
     from sleuth_b200.parts.spec import (AttentionSpec, EmbeddingSpec, GatedMLPSpec, HeadSpec, LayerSpec, ModelSpec,
                                         NormSpec, PositionSpec, ScheduleEntry)
     d = cfg.hidden_size
+    HD = cfg.head_dim
     pos = PositionSpec(head_dim=HD, theta=THETA)
     ffn = GatedMLPSpec(hidden=d, intermediate=INTER)
 
@@ -88,6 +116,8 @@ def toy_spec(cfg: ToyConfig, tensor_names=None):
         layer1 = LayerSpec(mixer=attn, ffn=Top1ExpertsSpec(d, EXPERT_INNER, EXPERTS), norm1=NormSpec(d, EPS),
                            norm2=NormSpec(d, EPS), names=n1)
         schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1))
+    elif cfg.variant == "learned":
+        layer1, schedule = None, None           # built below, with the toy ends
     elif cfg.variant == "state":
         layer1 = LayerSpec(mixer=RunningMeanSpec(d), ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS),
                            names=names(1, {"w.weight": "mean_mixer.w.weight"}))
@@ -99,8 +129,18 @@ def toy_spec(cfg: ToyConfig, tensor_names=None):
               "q_norm.weight": "self_attn.q_norm.weight"}
         layer1 = LayerSpec(mixer=reader, ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS), names=names(1, rn))
         schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 0))                           # layer 1 reads layer 0's cache
-    return ModelSpec(embedding=EmbeddingSpec(vocab=cfg.vocab_size, dim=d), layers=(layer0, layer1), schedule=schedule,
-                     head=HeadSpec(vocab=cfg.vocab_size, dim=d, norm=NormSpec(d, EPS), tied=True), max_positions=256)
+    embedding = EmbeddingSpec(vocab=cfg.vocab_size, dim=d)
+    head = HeadSpec(vocab=cfg.vocab_size, dim=d, norm=NormSpec(d, EPS), tied=True)
+    if cfg.variant == "learned":
+        # no rotation anywhere: positions come from a learned table in the embedding; the head is a toy kind too
+        nopos = PositionSpec(head_dim=HD, kind="none")
+        attn_np = AttentionSpec(hidden=d, heads=HEADS, kv_heads=KVH, head_dim=HD, position=nopos, qk_norm=True, qk_norm_eps=EPS)
+        layer0 = LayerSpec(mixer=attn_np, ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS), names=names(0, attn_names))
+        layer1 = LayerSpec(mixer=attn_np, ffn=ffn, norm1=NormSpec(d, EPS), norm2=NormSpec(d, EPS), names=names(1, attn_names))
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1))
+        embedding = LearnedPositionEmbeddingSpec(vocab=cfg.vocab_size, dim=d, positions=MAX_POS)
+        head = SoftcapHeadSpec(vocab=cfg.vocab_size, dim=d, norm=NormSpec(d, EPS), tied=True, cap=SOFTCAP)
+    return ModelSpec(embedding=embedding, layers=(layer0, layer1), schedule=schedule, head=head, max_positions=MAX_POS)
 
 
 def make_running_mean_mixer():
@@ -194,28 +234,86 @@ def make_scaled_rotary():
     return ScaledRotary
 
 
+def make_learned_position_embedding():
+    from sleuth_b200.parts.base import ParamDecl, Part
+
+    class LearnedPositionEmbedding(Part):
+        """x[t] = tokens[id of t] + positions[position of t]: it reads the batch's positions beside its token ids."""
+
+        def __init__(self, spec, ctx):
+            self.spec = spec
+
+        def declare(self):
+            return {"weight": ParamDecl((self.spec.vocab, self.spec.dim)),
+                    "positions.weight": ParamDecl((self.spec.positions, self.spec.dim))}
+
+        def bind(self, t):
+            self.table, self.positions = t["weight"], t["positions.weight"]       # ``table``: what a tied head reads
+
+        def forward(self, b, x):
+            ids = b.token_ids[:x.shape[0]] if b.ids_map is None else b.token_ids[b.ids_map[:x.shape[0]].long()]
+            x.copy_(self.table[ids.long()].float() + self.positions[b.tok_pos[:x.shape[0]].long()].float())
+
+    return LearnedPositionEmbedding
+
+
+def make_softcap_head():
+    from sleuth_b200.parts import build_norm
+    from sleuth_b200.parts.base import ParamDecl, Part
+
+    class SoftcapHead(Part):
+        """logits = cap * tanh((norm(x) @ W^T + bias) / cap) on the wanted rows."""
+
+        def __init__(self, spec, ctx):
+            self.spec, self.ctx = spec, ctx
+            self.norm = build_norm(spec.norm, ctx)
+
+        def declare(self):
+            d = {"norm.weight": ParamDecl((self.spec.dim,), "vector", init="gain"), "bias": ParamDecl((self.spec.vocab,), "vector")}
+            if not self.spec.tied:
+                d["weight"] = ParamDecl((self.spec.vocab, self.spec.dim))
+            return d
+
+        def bind(self, t, embedding_table=None):
+            self.norm.bind({"weight": t["norm.weight"]})
+            self.weight = embedding_table if self.spec.tied else t["weight"]
+            self.bias = t["bias"]
+
+        def forward(self, x, b, logits, ws):
+            h = torch.empty((logits.shape[0], self.spec.dim), dtype=self.ctx.dtype, device=x.device)
+            self.norm.forward(x, h, b.rows, b.stream)
+            raw = h.float() @ self.weight.float().T + self.bias
+            logits.copy_(self.spec.cap * torch.tanh(raw / self.spec.cap))
+
+    return SoftcapHead
+
+
 @pytest.fixture()
 def toy_registered():
     from sleuth_b200.config import register_architecture, unregister_architecture
-    from sleuth_b200.parts import register_ffn, register_mixer, register_position, unregister
+    from sleuth_b200.parts import (register_embedding, register_ffn, register_head, register_mixer, register_position,
+                                   unregister)
     register_mixer("running_mean", make_running_mean_mixer())
     register_ffn("top1_experts", make_top1_experts())
     register_position("scaled_rotary", make_scaled_rotary())
+    register_embedding("learned_position_embedding", make_learned_position_embedding())
+    register_head("softcap_head", make_softcap_head())
     register_architecture("ToyForCausalLM", ToyConfig, toy_spec, model_types=("toy",))
     yield
     unregister_architecture("ToyForCausalLM")
     unregister("mixer", "running_mean")
     unregister("ffn", "top1_experts")
     unregister("position", "scaled_rotary")
+    unregister("embedding", "learned_position_embedding")
+    unregister("head", "softcap_head")
 
 
-def settings():
+def settings(HD):
     return dict(d=HID, heads=HEADS, kv_heads=KVH, head_dim=HD, layers=2, eps=EPS, theta=THETA, tied=True, windows=[0, 0])
 
 
-def plain_state_model(w, ids):
-    s = settings()
-    w = {k: v.float() for k, v in w.items()}
+def plain_state_model(w, ids, HD=HD):
+    s = settings(HD)
     x = w["model.embed_tokens.weight"][torch.as_tensor(ids)]
     cos, sin = plain.rope_tables(HD, len(ids), THETA)
     x = plain.block(x, w, 0, s, cos, sin)
@@ -227,9 +325,8 @@ def plain_state_model(w, ids):
     return plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T
 
 
-def plain_shared_kv_model(w, ids):
-    s = settings()
-    w = {k: v.float() for k, v in w.items()}
+def plain_shared_kv_model(w, ids, HD=HD):
+    s = settings(HD)
     T = len(ids)
     x = w["model.embed_tokens.weight"][torch.as_tensor(ids)]
     cos, sin = plain.rope_tables(HD, T, THETA)
@@ -251,9 +348,8 @@ def plain_shared_kv_model(w, ids):
     return plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T
 
 
-def plain_routed_model(w, ids):
-    s = settings()
-    w = {k: v.float() for k, v in w.items()}
+def plain_routed_model(w, ids, HD=HD):
+    s = settings(HD)
     T = len(ids)
     x = w["model.embed_tokens.weight"][torch.as_tensor(ids)]
     # layer 0 by hand: its rotation is the toy one (scaled positions, the first ROT channels of a head only)
@@ -291,15 +387,50 @@ def plain_routed_model(w, ids):
     return plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T
 
 
+def plain_learned_model(w, ids, HD=HD):
+    T = len(ids)
+    x = w["model.embed_tokens.weight"][torch.as_tensor(ids)] + w["model.embed_positions.weight"][:T]
+    for i in range(2):
+        p = f"model.layers.{i}."
+        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], EPS)
+        q = (h @ w[p + "self_attn.q_proj.weight"].T).view(T, HEADS, HD).transpose(0, 1)
+        k = (h @ w[p + "self_attn.k_proj.weight"].T).view(T, KVH, HD).transpose(0, 1)
+        v = (h @ w[p + "self_attn.v_proj.weight"].T).view(T, KVH, HD).transpose(0, 1)
+        q = plain.rms_norm(q, w[p + "self_attn.q_norm.weight"], EPS)            # normalised, never rotated
+        k = plain.rms_norm(k, w[p + "self_attn.k_norm.weight"], EPS)
+        kk, vv = k.repeat_interleave(HEADS // KVH, 0), v.repeat_interleave(HEADS // KVH, 0)
+        sc = ((q @ kk.transpose(-2, -1)) / math.sqrt(HD)).masked_fill(~plain.causal_mask(T, 0), float("-inf"))
+        x = x + (sc.softmax(-1) @ vv).transpose(0, 1).reshape(T, HEADS * HD) @ w[p + "self_attn.o_proj.weight"].T
+        x = x + plain.swiglu(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], EPS), w, p + "mlp.")
+    raw = plain.rms_norm(x, w["model.norm.weight"], EPS) @ w["model.embed_tokens.weight"].T + w["lm_head.bias"]
+    return SOFTCAP * torch.tanh(raw / SOFTCAP)
+
+
+# float32: summation order only. bfloat16 (head size 64, so that the tensor-core attention kernels serve the toy
+# parts' layers): weights rounded alike on both sides, activations rounded in the engine only; the logits of these
+# models are below 1 in magnitude and the largest difference seen on a B200 was 0.012.
+TOY_TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=2.5e-2, atol=2.5e-2)}
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 @pytest.mark.parametrize("variant,oracle", [("state", plain_state_model), ("shared_kv", plain_shared_kv_model),
-                                            ("routed", plain_routed_model)])
-def test_toy_architecture_builds_loads_and_steps(variant, oracle, toy_registered, tmp_path):
+                                            ("routed", plain_routed_model), ("learned", plain_learned_model)])
+def test_toy_architecture_builds_loads_and_steps(variant, oracle, dtype, toy_registered, tmp_path):
+    import functools
+
     import sleuth_b200 as sb
     from sleuth_b200.cache.paged import KVRequest, StateRequest
-    cfg = dict(architectures=["ToyForCausalLM"], model_type="toy", vocab_size=VOCAB, hidden_size=HID, variant=variant)
+    hd = 16 if dtype == "fp32" else 64
+    cfg = dict(architectures=["ToyForCausalLM"], model_type="toy", vocab_size=VOCAB, hidden_size=HID, variant=variant,
+               head_dim=hd)
     folder = sb.write_random_model(tmp_path / variant, cfg, seed=3, dtype=torch.float32)
     _, w = plain.read_model(folder)
-    eng = sb.load(folder, dtype="fp32", max_seq_len=256, max_tokens=1024)
+    if dtype == "bf16":
+        w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    w = {k: v.float() for k, v in w.items()}
+    oracle = functools.partial(oracle, HD=hd)
+    tol = TOY_TOL[dtype]
+    eng = sb.load(folder, dtype=dtype, max_seq_len=256, max_tokens=1024)
     reqs = eng.model.cache_requests
     if variant == "state":
         assert "model.layers.1.mean_mixer.w.weight" in w
@@ -307,22 +438,52 @@ def test_toy_architecture_builds_loads_and_steps(variant, oracle, toy_registered
     elif variant == "routed":
         assert "model.layers.1.moe.experts.2.down.weight" in w and "model.layers.1.mlp.gate_proj.weight" not in w
         assert [type(r) for r in reqs] == [KVRequest, KVRequest]
+    elif variant == "learned":
+        assert w["model.embed_positions.weight"].shape == (MAX_POS, HID) and w["lm_head.bias"].shape == (VOCAB,)
+        assert type(eng.model.embedding).__name__ == "LearnedPositionEmbedding" and type(eng.model.head).__name__ == "SoftcapHead"
     else:
         assert "model.layers.1.self_attn.k_proj.weight" not in w and len(reqs) == 1     # one entry, written by layer 0
     rng = np.random.default_rng(1)
     a, b = rng.integers(0, VOCAB, size=70).tolist(), rng.integers(0, VOCAB, size=9).tolist()
     slots = eng.open(2)
     out = eng.step([(slots[0], a, tuple(range(70))), (slots[1], b, tuple(range(9)))]).cpu()
-    torch.testing.assert_close(out, torch.cat([oracle(w, a), oracle(w, b)]), rtol=1e-4, atol=2e-5)
+    want = torch.cat([oracle(w, a), oracle(w, b)])
+    print(f"toy {variant} {dtype}: largest difference {float((out - want).abs().max()):.3g}, largest logit {float(want.abs().max()):.3g}")
+    torch.testing.assert_close(out, want, **tol)
     eng.close(slots)
     # a reused slot starts from a zeroed state; prompt then token by token equals the whole sequence
     (slot,) = eng.open(1)
     assert slot in slots
     rows = [eng.step([(slot, a[:40], (39,))]).cpu()]
     rows += [eng.step([(slot, [t], (0,))]).cpu().clone() for t in a[40:]]
-    torch.testing.assert_close(torch.cat(rows), oracle(w, a)[39:], rtol=1e-4, atol=2e-5)
+    torch.testing.assert_close(torch.cat(rows), oracle(w, a)[39:], **tol)
     eng.close([slot])
     res = eng.generate([a[:5], b], max_new_tokens=4, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())
-    assert res[0].new_ids[0] == int(oracle(w, a[:5])[-1].argmax())
+    if dtype == "fp32":
+        assert res[0].new_ids[0] == int(oracle(w, a[:5])[-1].argmax())
     # parts that walk the step on the host or route by data are not recorded: no CUDA graph was made of a step
-    assert eng.model.capturable == (variant == "shared_kv") and (variant == "shared_kv" or not eng.stepper._graphs)
+    recorded = variant in ("shared_kv", "learned")
+    assert eng.model.capturable == recorded and (recorded or not eng.stepper._graphs)
+
+
+def test_state_is_sized_by_sequences_not_by_pages(toy_registered):
+    """A mixer that keeps a megabyte of state per sequence, in a cache of 4,096 pages: the state region holds as
+    many rows as sequences may be live at once, so it takes megabytes, not the 4 GB that a row per page would."""
+    from sleuth_b200.cache.paged import KVRequest, PagedCache, StateRequest
+    big = StateRequest((512, 512), torch.float32)                    # 1 MiB per sequence
+    reqs = [KVRequest(2, 16), big, None]
+    before = torch.cuda.memory_allocated()
+    cache = PagedCache(reqs, max_tokens=4096 * 64, max_seq_len=1024, dtype=torch.bfloat16, device="cuda:0", max_sequences=12)
+    assert cache.n_pages == 4096 and cache.max_slots == 12 and cache.states[1].shape == (12, 512, 512)
+    assert cache.book.max_slots == 12 and cache.book.groups[0].table.shape[0] == 12
+    default = PagedCache(reqs, max_tokens=4096 * 64, max_seq_len=1024, dtype=torch.bfloat16, device="cuda:0")
+    assert default.max_slots == 256 and default.states[1].numel() * 4 == 256 << 20
+    assert torch.cuda.memory_allocated() - before < (1 << 30)
+    assert PagedCache([KVRequest(2, 16)], 4096 * 64, 1024, torch.bfloat16, "cuda:0").max_slots == 4096    # no state: a slot per page
+    slots = cache.open(12)
+    with pytest.raises(Exception, match="slots"):
+        cache.open(1)
+    cache.states[1][slots[3]] += 1.0
+    cache.close(slots)
+    again = cache.open(12)
+    assert float(cache.states[1][again].abs().sum()) == 0.0            # a slot taken again starts from a zeroed state
