@@ -26,9 +26,10 @@ CONFIG = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               max_position_embeddings=4096)
 SEED = 606
 
-# float32: summation order only (the same bound as for the tiny models). bfloat16: weights rounded alike on both
-# sides, activations and cache entries rounded in the engine only.
-TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=4e-2, atol=4e-2)}
+# float32: summation order only (the same bound as for the tiny models; a B200 showed 1.0e-5 on logits up to 3.6).
+# bfloat16: weights rounded alike on both sides, activations and cache entries rounded in the engine only; the bound
+# is twice the largest difference seen on a B200 (0.038 on logits up to 3.6), absolute, with no relative part.
+TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=0.0, atol=7.5e-2)}
 
 
 @pytest.fixture(scope="module")

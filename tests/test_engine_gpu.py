@@ -15,10 +15,13 @@ from plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
 
-# Decided before the first run. float32: the engine and the plain code differ by summation order only.
-# bfloat16: weights are compared rounded alike, activations and cache entries are rounded in the engine
-# only; logits of these tiny models are of order 1.
-TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=4e-2, atol=4e-2)}
+# float32, decided before the first run: the engine and the plain code differ by summation order only (the largest
+# difference a B200 showed over all tests of this file: 1.2e-6 on logits up to 1.4).
+# bfloat16: weights are compared rounded alike, activations and cache entries are rounded in the engine only. The
+# bound is twice the largest difference seen on a B200 over all tests of this file (0.0085 on logits up to 1.4;
+# tests/closeness.py prints what a run saw), as an absolute bound with no relative part: a key rounded twice or a
+# gain applied in bfloat16 lies outside it.
+TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=0.0, atol=1.7e-2)}
 
 
 def load(folder, dtype, max_tokens=4096, **kw):
@@ -122,10 +125,10 @@ def test_long_decoding(dtype, model_folders):
         (ids,) = requests_for(name, [total], seed=5)
         (slot,) = eng.open(1)
         eng.step([(slot, ids[:7], ())])
-        check = {7, 8, 63, 64, 65, 127, 128, 200, 319, 320, total - 1}
+        look_at = {7, 8, 63, 64, 65, 127, 128, 200, 319, 320, total - 1}
         for t in range(7, total):
             out = eng.step([(slot, [ids[t]], (0,))])
-            if t in check:
+            if t in look_at:
                 check(out.cpu()[0], ref(ids)[t], TOL[dtype], "engine " + dtype)
         if name == "C":
             win = [g for g in eng.cache.book.groups if g.window][0]

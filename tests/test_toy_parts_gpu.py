@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 import torch
 
+from closeness import check
 from plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -448,15 +449,14 @@ def test_toy_architecture_builds_loads_and_steps(variant, oracle, dtype, toy_reg
     slots = eng.open(2)
     out = eng.step([(slots[0], a, tuple(range(70))), (slots[1], b, tuple(range(9)))]).cpu()
     want = torch.cat([oracle(w, a), oracle(w, b)])
-    print(f"toy {variant} {dtype}: largest difference {float((out - want).abs().max()):.3g}, largest logit {float(want.abs().max()):.3g}")
-    torch.testing.assert_close(out, want, **tol)
+    check(out, want, tol, "toy parts " + dtype)
     eng.close(slots)
     # a reused slot starts from a zeroed state; prompt then token by token equals the whole sequence
     (slot,) = eng.open(1)
     assert slot in slots
     rows = [eng.step([(slot, a[:40], (39,))]).cpu()]
     rows += [eng.step([(slot, [t], (0,))]).cpu().clone() for t in a[40:]]
-    torch.testing.assert_close(torch.cat(rows), oracle(w, a)[39:], **tol)
+    check(torch.cat(rows), oracle(w, a)[39:], tol, "toy parts " + dtype)
     eng.close([slot])
     res = eng.generate([a[:5], b], max_new_tokens=4, sampling=sb.SamplingConfig(temperature=0.0), stop_ids=())
     if dtype == "fp32":
