@@ -68,7 +68,8 @@ def test_trace_run_schedules(name, dtype, model_folders, tmp_path):
     # the most tokens live at once: a, b and c grown to their ends, each rounded up to 64
     out = tmp_path / "out"
     replay(model_folders[name], dtype, steps, out, max_tokens=128 + 64 + 64)
-    tol = dict(rtol=1e-4, atol=2e-5) if dtype == "float32" else dict(rtol=4e-2, atol=4e-2)
+    # the bounds of tests/test_engine_gpu.py: bfloat16 at twice the largest difference a B200 showed there
+    tol = dict(rtol=1e-4, atol=2e-5) if dtype == "float32" else dict(rtol=0.0, atol=1.7e-2)
     for step, rows in expect.items():
         got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), V)
         want = torch.stack([ref[r][p] for r, p in rows])
