@@ -14,11 +14,21 @@ rows whose logits are wanted only.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..parts import ends as _ends   # noqa: F401  (registers the token embedding and the output head)
 from ..parts.base import BuildContext, ParamDecl, build_embedding, build_head, build_layer, lead_weight_of
 from ..parts.spec import ModelSpec
+
+
+# How a step in which every sequence brings one token runs: "fused" = runs of layers whose parts offer it go through
+# the persistent kernel (csrc/decode_layers.cu), up to FUSED_DECODE_ROWS sequences; "kernels" = every layer launch
+# by launch, as steps of many tokens always run.
+DECODE_CHOICE = os.environ.get("SLEUTH_B200_DECODE", "kernels")
+FUSED_DECODE_ROWS = 16
+FUSED_DECODE_MIN_SLOTS = 5      # ring slots the kernel must have left beside the token rows in shared memory
 
 
 class Model:
@@ -37,6 +47,7 @@ class Model:
             self.entry_owner.setdefault(e.cache, i)
         self.cache_requests = [self.layers[spec.schedule[self.entry_owner[c]].layer].cache_request()
                                for c in range(len(self.entry_owner))]
+        self._programs: dict = {}       # per cache: the runs of the schedule prepared for the persistent kernel
 
     # ---- weights ----
     def _end_names(self, which: str) -> dict[str, str]:
@@ -85,16 +96,72 @@ class Model:
         x = ws.take((b.T, self.hidden), torch.float32)
         self.embedding.forward(b, x)
         schedule = self.spec.schedule
-        for i, e in enumerate(schedule):
+        fused = self._fused_runs(b, cache)
+        i = 0
+        while i < len(schedule):
+            if i in fused:
+                i = self._run_fused(fused[i], x, b, ws)
+                continue
+            e = schedule[i]
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
-            following = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            following = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) and (i + 1) not in fused else None
             b.next_read = lead_weight_of(following)
             self.layers[e.layer].forward(x, b, view, ws)
+            i += 1
         b.next_read = None
         if logits.shape[0]:
             self.head.forward(x, b, logits, ws)
         ws.release(mark)
         return logits
+
+    # ---- single-token steps through the persistent kernel ----
+    def _fused_runs(self, b, cache) -> dict:
+        """{first schedule index: (index after the run, program)} for this step, or {} when it does not qualify: every
+        sequence brings one token, at most FUSED_DECODE_ROWS of them, in bfloat16."""
+        if (DECODE_CHOICE != "fused" or self.ctx.dtype != torch.bfloat16 or b.max_count != 1 or b.T != b.n
+                or not 1 <= b.n <= FUSED_DECODE_ROWS):
+            return {}
+        runs = self._programs.get(id(cache))
+        if runs is None:
+            runs = self._programs[id(cache)] = self._prepare_runs(cache)
+        return {start: (end, prog) for start, end, prog in runs if prog.slots_for(b.n)[0] >= FUSED_DECODE_MIN_SLOTS}
+
+    def _prepare_runs(self, cache) -> list:
+        """Maximal runs of consecutive layer applications whose layers offer ``fused_decode`` and own their cache entry."""
+        from ..kernels import ops
+        runs, cur = [], []
+        schedule = self.spec.schedule
+
+        def close():
+            if cur:
+                prog = ops.decode_program([s for _, s, _ in cur], [v for _, _, v in cur], cache.pools)
+                if prog is not None:
+                    runs.append((cur[0][0], cur[-1][0] + 1, prog))
+                cur.clear()
+
+        for i, e in enumerate(schedule):
+            offer = getattr(self.layers[e.layer], "fused_decode", lambda: None)()
+            view = cache.view(e.cache, writes=True) if offer is not None and self.entry_owner[e.cache] == i else None
+            if offer is None or view is None or not hasattr(view, "k_pool"):
+                close()
+                continue
+            if cur and (offer["mixer"]["head_dim"] != cur[0][1]["mixer"]["head_dim"]):
+                close()
+            cur.append((i, offer, view))
+        close()
+        return runs
+
+    def _run_fused(self, run, x, b, ws) -> int:
+        from ..kernels import ops
+        end, prog = run
+        mark = ws.mark()
+        qkv = ws.take((b.n, prog.max_qkv), torch.bfloat16)
+        y = ws.take((b.n, prog.max_heads), torch.bfloat16)
+        act = ws.take((b.n, prog.max_inter), torch.bfloat16)
+        parts = ws.take((ops.decode_layers_scratch_floats(prog, b.n, ops.sm_count(x.device)),), torch.float32)
+        ops.decode_layers(prog, x, b.past, b.tables, qkv, y, act, parts, b.stream, trace=getattr(self, "decode_trace", None))
+        ws.release(mark)
+        return end
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

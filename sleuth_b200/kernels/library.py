@@ -144,6 +144,7 @@ _SIGNATURES = {
     "slb_gemm_skinny_norm": [P, P, F, P, P, I, I, I, I, I, P, L, P, P],
     "slb_gemm_tc": [P, P, P, I, I, I, I, I, P, P],
     "slb_tc_wait_probe": [P, I, I, P],
+    "slb_decode_layers": [P, P],
     "slb_gemm_tc_qkv": [P, P, I, I, I, I, I, P, P, P, P, P, F, P, P, P, P, P, P, I, P, P],
     "slb_gemm_f32": [P, P, P, P, I, I, I, I, I, I, I, P],
     "slb_penalize": [P, L, I, I, P, P, I, F, P, P, I, P],

@@ -437,8 +437,154 @@ def gemm_tc_check(device) -> None:
         st.zero_()
         raise RuntimeError(f"a wait inside a tcgen05 kernel gave up (code {code}; product: 1 = free stage, 2 = loaded "
                            f"stage, 3 = finished accumulator, 4 = drained accumulator; attention: 20 = shared memory "
-                           f"misaligned, 21-27 = producer and MMA waits, 28-32 = softmax waits; 99 = the wait probe of the tests); "
+                           f"misaligned, 21-27 = producer and MMA waits, 28-32 = softmax waits; persistent single-token kernel: 40 = grid "
+                           f"barrier, 41 = a ring slot that did not fill, 42 = a ring slot that did not empty; 99 = the wait "
+                           f"probe of the tests); "
                            f"its results are not valid")
+
+
+# ---------------------------------------------------------------- the persistent single-token kernel ----
+_VP, _LL, _CI, _CF = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+DL_MAX_PLANS, DL_MAX_ROWS, DL_MAX_UNITS, DL_MAX_GROUP = 4, 16, 256, 8
+
+
+class _DlLayer(ctypes.Structure):          # mirrors DlLayer in csrc/decode_layers.cu
+    _fields_ = [(n, _VP) for n in ("w_qkv", "w_o", "w_gu", "w_down", "norm1", "norm2", "bias", "q_gain", "k_gain", "cos_table",
+                                   "sin_table", "k_pool", "v_pool")] + \
+               [("k_row0", _LL), ("v_row0", _LL), ("eps1", _CF), ("eps2", _CF), ("qk_eps", _CF), ("scale_log2", _CF),
+                ("heads", _CI), ("kv_heads", _CI), ("inter", _CI), ("window", _CI), ("group", _CI), ("plan", _CI),
+                ("pad0", _CI), ("pad1", _CI)]
+
+
+class _DlArgs(ctypes.Structure):           # mirrors DlArgs
+    _fields_ = [(n, _VP) for n in ("layers", "x", "qkv", "y", "act", "parts", "tickets", "barrier", "status", "past", "trace")] + \
+               [("tables", _VP * 2), ("table_stride", _CI * 2), ("plan_window", _CI * DL_MAX_PLANS),
+                ("plan_kv_heads", _CI * DL_MAX_PLANS), ("n_plans", _CI), ("n_layers", _CI), ("B", _CI), ("d", _CI),
+                ("n_slots", _CI), ("stage_bytes", _CI)]
+
+
+class _DlHost(ctypes.Structure):           # mirrors DlHost
+    _fields_ = [("args", _DlArgs), ("pool_base", _VP * 2), ("pool_rows", _LL * 2), ("head_dim", _CI), ("n_groups", _CI)]
+
+
+class DecodeProgram:
+    """A run of layers prepared for ``decode_layers``: the layers' descriptions in device memory and what is the same
+    for every launch. Built by ``decode_program`` from what the layers' parts offer (``Part.fused_decode``)."""
+
+    def __init__(self, layers_dev, n_layers, head_dim, hidden, kmax, max_qkv, max_heads, max_inter, plans, groups, keep):
+        self.layers_dev, self.n_layers, self.head_dim, self.hidden, self.kmax = layers_dev, n_layers, head_dim, hidden, kmax
+        self.max_qkv, self.max_heads, self.max_inter = max_qkv, max_heads, max_inter
+        self.plans, self.groups, self.keep = plans, groups, keep
+        device = layers_dev.device
+        self.tickets = torch.zeros(DL_MAX_UNITS, dtype=torch.int32, device=device)
+        self.barrier = torch.zeros(4, dtype=torch.int32, device=device)
+        self._slots: dict = {}
+
+    def slots_for(self, rows: int) -> tuple[int, int]:
+        """(ring slots, bytes of the staging area) for a step of ``rows`` sequences; fewer than 4 slots: do not fuse."""
+        if rows not in self._slots:
+            dll = lib().dll
+            dll.slb_decode_layers_stage_bytes.restype = ctypes.c_int
+            dll.slb_decode_layers_slots.restype = ctypes.c_int
+            stage = int(dll.slb_decode_layers_stage_bytes(int(rows), int(self.kmax), int(self.head_dim)))
+            self._slots[rows] = (int(dll.slb_decode_layers_slots(stage)), stage)
+        return self._slots[rows]
+
+
+def decode_program(shares: list, views: list, pools: list) -> DecodeProgram | None:
+    """Prepare a run of layers for the persistent single-token kernel. ``shares``: per layer what its parts offer
+    (``PreNormLayer.fused_decode``); ``views``: per layer the ``KVView`` of its cache entry; ``pools``: the cache's
+    pool tensor of each group. None when the run does not fit the kernel (mixed head sizes or widths, more than two
+    cache groups or four page plans)."""
+    if not shares:
+        return None
+    hd = shares[0]["mixer"]["head_dim"]
+    d = shares[0]["mixer"]["hidden"]
+    group_ids, plans, keep = [], [], []
+    arr = (_DlLayer * len(shares))()
+    kmax = max_qkv = max_heads = max_inter = 0
+    for i, (sh, view) in enumerate(zip(shares, views)):
+        m, f = sh["mixer"], sh["ffn"]
+        if m["head_dim"] != hd or m["hidden"] != d or view is None or not getattr(view, "writes", False):
+            return None
+        if view.group not in group_ids:
+            group_ids.append(view.group)
+        plan = (int(m["window"]), int(m["kv_heads"]))
+        if plan not in plans:
+            plans.append(plan)
+        if len(group_ids) > 2 or len(plans) > DL_MAX_PLANS:
+            return None
+        pool = pools[view.group]
+        L = arr[i]
+        for name, t in (("w_qkv", m["w_qkv"]), ("w_o", m["w_o"]), ("w_gu", f["w_gu"]), ("w_down", f["w_down"]),
+                        ("norm1", sh["norm1"]["gain"]), ("norm2", sh["norm2"]["gain"]), ("bias", m["bias"]),
+                        ("q_gain", m["q_gain"]), ("k_gain", m["k_gain"]), ("cos_table", m["cos"]), ("sin_table", m["sin"]),
+                        ("k_pool", view.k_pool), ("v_pool", view.v_pool)):
+            if t is not None:
+                _need(t.is_cuda and t.is_contiguous() and t.data_ptr() % 16 == 0, f"decode_program: {name} must be a contiguous, aligned CUDA tensor")
+                keep.append(t)
+            setattr(L, name, _p(t))
+        for t in (m["w_qkv"], m["w_o"], f["w_gu"], f["w_down"], view.k_pool):
+            _need(t.dtype == torch.bfloat16, "decode_program: matrices and the cache are bfloat16")
+        for t in (sh["norm1"]["gain"], sh["norm2"]["gain"], m["bias"], m["q_gain"], m["k_gain"], m["cos"], m["sin"]):
+            _need(t is None or t.dtype == torch.float32, "decode_program: gains, biases and tables are float32")
+        row_bytes = hd * 2
+        L.k_row0 = (view.k_pool.data_ptr() - pool.data_ptr()) // row_bytes
+        L.v_row0 = (view.v_pool.data_ptr() - pool.data_ptr()) // row_bytes
+        L.eps1, L.eps2, L.qk_eps = float(sh["norm1"]["eps"]), float(sh["norm2"]["eps"]), float(m["qk_eps"])
+        L.scale_log2 = float(m["scale"]) * 1.4426950408889634
+        L.heads, L.kv_heads, L.inter, L.window = int(m["heads"]), int(m["kv_heads"]), int(f["inter"]), int(m["window"])
+        L.group, L.plan = group_ids.index(view.group), plans.index(plan)
+        n_qkv = (L.heads + 2 * L.kv_heads) * hd
+        _need(tuple(m["w_qkv"].shape) == (n_qkv, d) and tuple(m["w_o"].shape) == (d, L.heads * hd) and
+              tuple(f["w_gu"].shape) == (2 * L.inter, d) and tuple(f["w_down"].shape) == (d, L.inter),
+              "decode_program: weight shapes disagree with the sizes")
+        kmax = max(kmax, d, L.heads * hd, L.inter)
+        max_qkv, max_heads, max_inter = max(max_qkv, n_qkv), max(max_heads, L.heads * hd), max(max_inter, L.inter)
+    device = shares[0]["mixer"]["w_qkv"].device
+    raw = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(device)
+    groups = [(pools[g], pools[g].numel() // hd) for g in group_ids]
+    keep.extend(p for p, _ in groups)
+    return DecodeProgram(raw, len(shares), hd, d, kmax, max_qkv, max_heads, max_inter, plans, [(gid, *g) for gid, g in zip(group_ids, groups)], keep)
+
+
+def decode_layers_scratch_floats(prog: DecodeProgram, rows: int, blocks: int) -> int:
+    return (blocks + DL_MAX_UNITS) * (DL_MAX_GROUP * prog.head_dim + 2 * DL_MAX_GROUP)
+
+
+def decode_layers(prog: DecodeProgram, x: torch.Tensor, past: torch.Tensor, tables: list, qkv, y, act, parts, stream=None,
+                  trace: torch.Tensor | None = None) -> None:
+    """Run the program's layers on the float32 stream ``x [B, hidden]`` of a step in which each of the B sequences
+    brings one token: ``past [B]`` their positions, ``tables`` the step's block table of every cache group
+    (indexed as the cache indexes its groups). ``qkv``, ``y``, ``act`` (bfloat16) and ``parts`` (float32) are scratch.
+    ``trace``: None, or an int64 tensor [blocks, layers, 16] that receives every block's nanosecond stamps at the phase
+    boundaries of every layer (a diagnostic: where the step's time goes)."""
+    _cuda(x, past, qkv, y, act, parts)
+    B, d = x.shape
+    _need(x.dtype == torch.float32 and d == prog.hidden and 1 <= B <= DL_MAX_ROWS, "decode_layers: x is float32 [1..16, hidden]")
+    n_slots, stage = prog.slots_for(B)
+    _need(n_slots >= 4, "decode_layers: the token rows leave no room for the ring in shared memory")
+    blocks = sm_count(x.device)
+    _need(qkv.numel() >= B * prog.max_qkv and y.numel() >= B * prog.max_heads and act.numel() >= B * prog.max_inter and
+          parts.numel() >= decode_layers_scratch_floats(prog, B, blocks) and qkv.dtype == y.dtype == act.dtype == torch.bfloat16
+          and parts.dtype == torch.float32, "decode_layers: scratch buffers are too small or of the wrong dtype")
+    h = _DlHost()
+    a = h.args
+    a.layers, a.x, a.qkv, a.y, a.act, a.parts = prog.layers_dev.data_ptr(), x.data_ptr(), qkv.data_ptr(), y.data_ptr(), act.data_ptr(), parts.data_ptr()
+    a.tickets, a.barrier, a.status, a.past = prog.tickets.data_ptr(), prog.barrier.data_ptr(), _tc_status(x.device).data_ptr(), past.data_ptr()
+    if trace is not None:
+        _need(trace.is_cuda and trace.dtype == torch.int64 and trace.numel() >= blocks * prog.n_layers * 16, "decode_layers: trace is int64 [blocks, layers, 16]")
+    a.trace = _p(trace)
+    for i, (gid, pool, rows) in enumerate(prog.groups):
+        t = tables[gid]
+        _need(t.dtype == torch.int32 and t.dim() == 2 and t.shape[0] >= B and t.is_contiguous(), "decode_layers: block tables are int32 [B, stride]")
+        a.tables[i], a.table_stride[i] = t.data_ptr(), t.shape[1]
+        h.pool_base[i], h.pool_rows[i] = pool.data_ptr(), rows
+    for i, (window, kvh) in enumerate(prog.plans):
+        a.plan_window[i], a.plan_kv_heads[i] = window, kvh
+    a.n_plans, a.n_layers, a.B, a.d, a.n_slots, a.stage_bytes = len(prog.plans), prog.n_layers, B, d, n_slots, stage
+    h.head_dim, h.n_groups = prog.head_dim, len(prog.groups)
+    lib().call("slb_decode_layers", ctypes.addressof(h), stream if stream is not None else current_stream())
 
 
 def penalize(logits, limit: int, recent, n_recent, penalty: float, banned, n_banned, stream=None) -> None:

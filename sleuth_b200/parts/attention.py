@@ -111,6 +111,19 @@ class GQAAttention(Part):
     def lead_weight(self):
         return self.qkv.weight if self.qkv is not None else None
 
+    def fused_decode(self):
+        s = self.spec
+        rot = self.position.rot_dim
+        if (self.ctx.dtype != torch.bfloat16 or self.qkv is None or s.reads_shared_kv or s.head_dim not in (64, 128)
+                or rot not in (0, s.head_dim) or s.heads // s.kv_heads > 8 or s.hidden % 128
+                or (s.qk_norm and (self.q_gain is None or self.k_gain is None))):
+            return None
+        tables = self.position.tables() if rot else None
+        return {"w_qkv": self.qkv.weight, "w_o": self.o.weight, "bias": self.bias, "q_gain": self.q_gain if s.qk_norm else None,
+                "k_gain": self.k_gain if s.qk_norm else None, "cos": tables[0] if tables else None,
+                "sin": tables[1] if tables else None, "heads": s.heads, "kv_heads": s.kv_heads, "head_dim": s.head_dim,
+                "window": s.window, "qk_eps": s.qk_norm_eps, "scale": self.scale, "hidden": s.hidden}
+
     def forward(self, h, x, b, view, ws):
         s = self.spec
         T = h.shape[0]

@@ -96,6 +96,13 @@ class Part:
     def cache_request(self):
         return None
 
+    def fused_decode(self):
+        """What the persistent single-token kernel (``csrc/decode_layers.cu``) needs of this part, as a dictionary of
+        tensors and constants, or None when the part cannot take part in it (the layer then runs launch by launch).
+        The built-in RMSNorm, grouped-query attention, gated feed-forward and pre-norm layer answer; a part that
+        says nothing is simply not fused."""
+        return None
+
     def lead_weight(self):
         """The weight matrix that this part's first product reads, or None. The part that runs before this one may
         hand it to its last kernel, which then asks the L2 cache for it (``StepBatch.next_read``)."""

@@ -41,6 +41,11 @@ class GatedMLP(Part):
     def lead_weight(self):
         return self.gate_up.weight if self.gate_up is not None else None
 
+    def fused_decode(self):
+        if self.ctx.dtype != torch.bfloat16 or self.gate_up is None or self.spec.intermediate % 32 or self.spec.hidden % 128:
+            return None
+        return {"w_gu": self.gate_up.weight, "w_down": self.down.weight, "inter": self.spec.intermediate}
+
     def forward(self, h, x, b, ws):
         T = h.shape[0]
         mark = ws.mark()

@@ -38,6 +38,16 @@ class PreNormLayer(Part):
     def lead_weight(self):
         return lead_weight_of(self.mixer)
 
+    def fused_decode(self):
+        """x += mixer(norm1(x)); x += ffn(norm2(x)) is what the persistent single-token kernel runs: offered when all
+        four parts offer their share."""
+        shares = {name: getattr(part, "fused_decode", lambda: None)() for name, part in self.children.items()}
+        if any(v is None for v in shares.values()):
+            return None
+        if "w_qkv" not in shares["mixer"] or "w_gu" not in shares["ffn"] or "gain" not in shares["norm1"] or "gain" not in shares["norm2"]:
+            return None
+        return shares
+
     def forward(self, x, b, view, ws):
         mark = ws.mark()
         after = getattr(b, "next_read", None)    # what follows this layer

@@ -23,6 +23,9 @@ class RMSNorm(Part):
     def bind(self, tensors):
         self.weight = tensors["weight"]
 
+    def fused_decode(self):
+        return {"gain": self.weight, "eps": self.eps} if self.weight is not None else None
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, stream=None):
         """out[r] = norm(x[rows[r]]) (or x[r] without ``rows``); ``out`` has the run dtype."""
         ops.rmsnorm(x, self.weight, out, self.eps, rows, stream)

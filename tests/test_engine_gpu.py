@@ -48,11 +48,11 @@ def requests_for(name, lengths, seed=0):
 
 
 LENGTHS = {"A": [5, 11, 17, 70], "B": [1, 7, 23, 40, 130], "C": [3, 64, 65, 150, 33], "D": [40, 1, 200, 129],
-           "E": [10, 140, 300, 129]}
+           "E": [10, 140, 300, 129], "F": [10, 140, 300, 129, 65], "G": [33, 1, 200, 700]}
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G"])
 def test_each_request_alone_and_whole(name, dtype, model_folders):
     eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
     for ids in requests_for(name, LENGTHS[name]):
@@ -63,7 +63,7 @@ def test_each_request_alone_and_whole(name, dtype, model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G"])
 def test_last_32_tokens_one_by_one(name, dtype, model_folders):
     eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
     for ids in requests_for(name, [n for n in LENGTHS[name] if n > 32] + [33]):
@@ -77,7 +77,7 @@ def test_last_32_tokens_one_by_one(name, dtype, model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "G"])
 def test_unequal_batches_one_after_another_reuse_slots(name, dtype, model_folders):
     """Three batches through a cache with room for one batch only. Within a batch the requests have unequal
     prompts and unequal numbers of decoded tokens, so the shorter ones end earlier; the next batch gets
@@ -120,7 +120,7 @@ def test_unequal_batches_one_after_another_reuse_slots(name, dtype, model_folder
 def test_long_decoding(dtype, model_folders):
     """600 tokens decoded one by one after a short prompt: positions cross nine pages, the decode step runs
     as a captured graph from its second occurrence on, and the window layers of C drop pages on the way."""
-    for name, total in (("D", 640), ("C", 330)):
+    for name, total in (("D", 640), ("C", 330), ("F", 400), ("G", 640)):
         eng, ref = load(model_folders[name], dtype, max_tokens=1024), oracle(model_folders[name], dtype)
         (ids,) = requests_for(name, [total], seed=5)
         (slot,) = eng.open(1)
@@ -130,14 +130,14 @@ def test_long_decoding(dtype, model_folders):
             out = eng.step([(slot, [ids[t]], (0,))])
             if t in look_at:
                 check(out.cpu()[0], ref(ids)[t], TOL[dtype], "engine " + dtype)
-        if name == "C":
+        if name in ("C", "F"):
             win = [g for g in eng.cache.book.groups if g.window][0]
-            assert (win.table[slot] >= 0).sum() <= 2          # 40 keys never need more than two pages
+            assert (win.table[slot] >= 0).sum() <= (2 if name == "C" else 3)     # 40 (70) keys never need more pages
         eng.close([slot])
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "F", "G"])
 def test_first_tokens(name, dtype, model_folders):
     eng, ref = load(model_folders[name], dtype), oracle(model_folders[name], dtype)
     (ids,) = requests_for(name, [4], seed=9)
@@ -249,7 +249,7 @@ def test_greedy_generation_through_the_entry_point(name, model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["B", "D", "E"])
+@pytest.mark.parametrize("name", ["B", "D", "E", "F", "G"])
 def test_device_fed_decode_steps_give_the_plain_logits(name, dtype, model_folders):
     """The pipelined loop's steps, driven by hand: the prompt step, the choice left in the device-side feed
     (``choose_later``), then ``decode_fed`` steps that take their tokens from that feed through an index map, with a

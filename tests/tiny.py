@@ -2,7 +2,8 @@
 query and key/value heads (and so the group size), head size (16, 24 with heads * head_dim != width,
 64 for the tensor-core kernels, 32), intermediate size, vocabulary (no power of two in B and C),
 rope_theta, rms_norm_eps, q/k/v biases, tied or separate output matrix, context, and a sliding
-window on some layers (C)."""
+window on some layers (C, E, F). F and G have the sizes that send their single-token steps through the
+persistent kernel."""
 
 A = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256, hidden_size=64,
          intermediate_size=192, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
@@ -35,5 +36,20 @@ E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777,
          max_position_embeddings=512, sliding_window=48,
          layer_types=["full_attention", "sliding_attention", "full_attention"])
 
-CONFIGS = {"A": A, "B": B, "C": C, "D": D, "E": E}
-SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44, "E": 55}
+# Sizes that the persistent single-token kernel takes (width a multiple of 128, head size 64, intermediate a multiple
+# of 32): decode steps of up to 16 sequences of this one run through it, with biases, a group of 2 and a window on the
+# middle layer
+F = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=333, hidden_size=128,
+         intermediate_size=96, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+         rope_theta=500000.0, rms_norm_eps=1e-5, attention_bias=True, tie_word_embeddings=False,
+         max_position_embeddings=512, sliding_window=70,
+         layer_types=["full_attention", "sliding_attention", "full_attention"])
+
+# The same kernel at head size 128 with a group of 3, no biases, no window, a wider intermediate
+G = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=410, hidden_size=256,
+         intermediate_size=160, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+         rope_theta=20000.0, rms_norm_eps=3e-6, attention_bias=False, tie_word_embeddings=True,
+         max_position_embeddings=1024)
+
+CONFIGS = {"A": A, "B": B, "C": C, "D": D, "E": E, "F": F, "G": G}
+SEEDS = {"A": 11, "B": 22, "C": 33, "D": 44, "E": 55, "F": 66, "G": 77}
