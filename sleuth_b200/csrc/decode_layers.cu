@@ -28,6 +28,15 @@
 // Every wait is a bounded poll (mbarriers, the grid barrier): one that runs out records a code in `status`, raises
 // an abort word that the other blocks see at their next barrier, and the block drains its copies in flight and
 // returns. No TMA load uses cluster multicast.
+//
+// Where it stands. The kernel is correct (it is tested against the plain implementation like the separate kernels)
+// and it is NOT the default: on a B200 with the Qwen3-0.6B shapes a layer takes 39 us at batch 1 and 61 us at batch 8
+// against 25 and 33 us launch by launch. A launch may be given a trace buffer (DlArgs::trace), which says where the
+// time goes: the stream is never the limit (a phase waits 0.2-0.5 us for its data, attention at batch 8 3.4 us); a
+// grid barrier costs 2.0-2.5 us, five times a layer, as much as the kernel boundaries it replaces; and between the
+// barriers eight warps per SM walk through each phase as one chain of dependent instructions (0.2 instructions a
+// cycle and scheduler; the separate kernels keep 12 to 24 independent warps on an SM). The engine runs it when
+// SLEUTH_B200_DECODE=fused.
 #include <math.h>
 
 #include "mma_sync.cuh"
@@ -45,6 +54,9 @@ constexpr int kDlMaxSlots = 12;
 constexpr int kDlMaxUnits = 256;                     // (sequence, kv head) pairs
 constexpr int kDlMaxPlans = 4;                       // distinct (window, kv heads) among the layers
 constexpr int kDlMaxGroup = 8;                       // query heads per kv head
+constexpr int kDlMaxAcc = 8;                         // output tiles (gate and up counted apart) a block multiplies before it adds up the warps
+constexpr int kDlMaxCombos = 4;                      // distinct (page plan, cache group) among the layers
+constexpr int kDlMaxRun = 192;                       // pages of a block's run whose places are looked up ahead of time
 constexpr uint32_t kDlBarrierPolls = 4000000u;
 
 // What is fixed per layer (an array of these lives in device memory).
@@ -68,7 +80,8 @@ struct DlLayer {
   int heads, kv_heads, inter, window;
   int group;                     // which block table and tensor map
   int plan;                      // which page plan (window, kv heads)
-  int pad0, pad1;
+  int combo;                     // which (plan, group) pair: the producer keeps a list of page places for each
+  int pad1;
 };
 
 // What a launch brings.
@@ -83,24 +96,28 @@ struct DlArgs {
   unsigned int* barrier;         // [0] arrivals, [1] abort word; zeroed before the launch
   int* status;                   // 0, or the code of a wait that gave up
   const int* past;               // [B] position of each sequence's new token
-  unsigned long long* trace;     // null, or [blocks][layers][16] nanosecond stamps: where a step's time goes (diagnostic)
+  unsigned long long* trace;     // null, or [blocks][layers][24]: nanosecond stamps and waiting cycles: where a step's time goes (diagnostic)
   const int* tables[2];          // block table of each cache group [B, table_stride]
   int table_stride[2];
   int plan_window[kDlMaxPlans], plan_kv_heads[kDlMaxPlans];
-  int n_plans, n_layers, B, d, n_slots, stage_bytes;
+  int combo_plan[kDlMaxCombos], combo_group[kDlMaxCombos];
+  int n_plans, n_combos, n_layers, B, d, n_slots, stage_bytes, pad;
 };
 
 struct DlCtx {
   unsigned char* ring;           // n_slots slots
   unsigned char* stage;          // the A operand of a product (token rows, bfloat16), or the merge area of attention
-  float* red;                    // [2][2][8 warps][16][9] partial sums of a tile
+  float* red;                    // [kDlMaxAcc][8 warps][B][9] partial sums of the tiles of a pass
   unsigned char* sq;             // [16][hd] query rows, swizzled
-  float* ss;                     // [16][8] partial sums of squares
+  float* ss;                     // [16][8] partial sums of squares of the rows being normalised
   const int* pre;                // [plans][kDlMaxUnits + 1] first page of each unit in the flattened list
+  const int* past;               // [B] the sequences' positions, in shared memory
+  int norm_parts;                // pieces each row's sum of squares came in
   int* flag;                     // [0] ticket or barrier verdict (consumers), [1] block-wide abort
   uint32_t full0, empty0;        // shared-memory addresses of the slots' barriers
   unsigned int fill;             // slots consumed (or produced) so far
   unsigned int epoch;            // grid barriers passed
+  long long waited;              // clock cycles spent waiting for slots to fill (diagnostic, read by traced launches)
   int rot;                       // whose turn the next product's first tile is
   int red_buf;
   int cta, nblocks, n_slots;
@@ -111,8 +128,13 @@ __device__ __forceinline__ void dl_stamp(const DlArgs& a, int layer, int i) {
   if (a.trace != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    a.trace[((size_t)blockIdx.x * a.n_layers + layer) * 16 + i] = t;
+    a.trace[((size_t)blockIdx.x * a.n_layers + layer) * 24 + i] = t;
   }
+}
+// ... and the cycles the phase that just ended spent waiting for its slots
+__device__ __forceinline__ void dl_stamp_wait(const DlArgs& a, DlCtx& c, int layer, int i) {
+  if (a.trace != nullptr && threadIdx.x == 0) a.trace[((size_t)blockIdx.x * a.n_layers + layer) * 24 + i] = (unsigned long long)c.waited;
+  c.waited = 0;
 }
 
 __device__ __forceinline__ void dl_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kDlConsumers) : "memory"); }
@@ -131,7 +153,12 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
 // ------------------------------------------------------------------------------------ consumers: the ring ----
 __device__ __forceinline__ bool slot_wait(const DlArgs& a, DlCtx& c, unsigned int fill) {
   const unsigned int s = fill % c.n_slots;
-  if (mbar_wait(c.full0 + 8 * s, (fill / c.n_slots) & 1)) return true;
+  if (a.trace != nullptr) {
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(c.full0 + 8 * s, (fill / c.n_slots) & 1);
+    c.waited += clock64() - t0;
+    if (ok) return true;
+  } else if (mbar_wait(c.full0 + 8 * s, (fill / c.n_slots) & 1)) return true;
   dl_fail(a, c, 41);
   return false;
 }
@@ -140,13 +167,14 @@ __device__ __forceinline__ void slot_release(DlCtx& c, unsigned int fill) {
   if ((threadIdx.x & 31) == 0) mbar_arrive(c.empty0 + 8 * (fill % c.n_slots));
 }
 
-// All blocks meet. Returns false when the wait ran out or another block gave up.
+// All blocks meet. Returns false when the wait ran out or another block gave up. The consumers' barrier in front
+// orders every thread's stores before thread 0's arrival, which releases them at device scope; the poll acquires the
+// other blocks' stores, and the barrier behind hands them on to the block's threads.
 __device__ bool grid_barrier(const DlArgs& a, DlCtx& c) {
   dl_bar();
   if (threadIdx.x == 0) {
     int ok = 1;
-    __threadfence();
-    atomicAdd(a.barrier, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier) : "memory");
     const unsigned int target = (c.epoch + 1) * (unsigned int)c.nblocks;
     uint32_t polls = 0;
     for (;;) {
@@ -163,55 +191,63 @@ __device__ bool grid_barrier(const DlArgs& a, DlCtx& c) {
         }
       }
     }
-    __threadfence();
     c.flag[0] = ok;
   }
   dl_bar();
   ++c.epoch;
-  const bool ok = c.flag[0] != 0 && c.flag[1] == 0;
-  dl_bar();
-  return ok;
+  // (thread 0 writes flag[0] again only behind a later barrier of the consumers, which every thread reaches after this read)
+  return c.flag[0] != 0 && c.flag[1] == 0;
 }
 
 // ------------------------------------------------------------------------------------ staging the token rows ----
 __device__ __forceinline__ int stage_stride(int kdim) { return ((kdim * 2 + 127) & ~127) + 64; }
 
-// stage[r] = bfloat16(rmsnorm(x[r]; gain, eps)) for the B rows of the float32 stream.
-__device__ void stage_norm(const DlArgs& a, DlCtx& c, const float* gain, float eps) {
+// The rows of the float32 stream on their way into a product that follows an RMSNorm
+// (y = (x / sqrt(mean(x^2) + eps)) * gain): stage[r] = bfloat16(x[r] * gain), and the pieces of each row's sum of
+// squares go to `ss`; the factor 1 / rms, one number per row, multiplies the product's float32 sums instead of its
+// inputs (`row_scale`), so the rows are read once and nothing waits for the sum. All loads of a lane go out together.
+__device__ void stage_scaled(const DlArgs& a, DlCtx& c, const float* gain) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = a.d, B = a.B, AS = stage_stride(d);
   // a row is cut into `parts` pieces, one per warp, when there are fewer rows than warps
   int parts = 1;
   while (parts * 2 * B <= kDlConsumerWarps && (d / (parts * 2)) % 128 == 0) parts *= 2;
-  const int seg = d / parts;
+  c.norm_parts = parts;
+  const int seg = d / parts, n4 = seg / 4;
   for (int r0 = 0; r0 < B; r0 += kDlConsumerWarps / parts) {
     const int r = r0 + warp / parts, part = warp % parts;
-    const bool live = r < B;
-    float ssq = 0.0f;
-    if (live) {
+    if (r < B) {
       const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)r * d + part * seg);
-      for (int i = lane; i < seg / 4; i += 32) {
-        const float4 v = __ldcg(src + i);
-        ssq += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+      const float4* gn = reinterpret_cast<const float4*>(gain + part * seg);
+      uint2* dst = reinterpret_cast<uint2*>(c.stage + (size_t)r * AS + (size_t)part * seg * 2);
+      float ssq = 0.0f;
+      for (int i0 = 0; i0 < n4; i0 += 8 * 32) {
+        float4 v[8], g4[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          v[j] = i < n4 ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          g4[j] = i < n4 ? gn[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          ssq += (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+          if (i < n4) dst[i] = make_uint2(pack_bf16(v[j].x * g4[j].x, v[j].y * g4[j].y), pack_bf16(v[j].z * g4[j].z, v[j].w * g4[j].w));
+        }
       }
       ssq = warp_sum(ssq);
       if (lane == 0) c.ss[(r & 15) * 8 + part] = ssq;
     }
-    dl_bar();
-    if (live) {
-      float tot = 0.0f;
-      for (int p = 0; p < parts; ++p) tot += c.ss[(r & 15) * 8 + p];
-      const float inv = 1.0f / sqrtf(tot / (float)d + eps);
-      const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)r * d + part * seg);
-      const float4* gn = reinterpret_cast<const float4*>(gain + part * seg);
-      uint2* dst = reinterpret_cast<uint2*>(c.stage + (size_t)r * AS + (size_t)part * seg * 2);
-      for (int i = lane; i < seg / 4; i += 32) {
-        const float4 v = __ldcg(src + i), g4 = gn[i];
-        dst[i] = make_uint2(pack_bf16((v.x * inv) * g4.x, (v.y * inv) * g4.y), pack_bf16((v.z * inv) * g4.z, (v.w * inv) * g4.w));
-      }
-    }
-    dl_bar();
   }
+  dl_bar();
+}
+
+// 1 / rms of row r, from the pieces stage_scaled left (added in a fixed order)
+__device__ __forceinline__ float row_scale(const DlArgs& a, const DlCtx& c, int r, float eps) {
+  float tot = 0.0f;
+  for (int p = 0; p < c.norm_parts; ++p) tot += c.ss[(r & 15) * 8 + p];
+  return 1.0f / sqrtf(tot / (float)a.d + eps);
 }
 
 // stage[r] = src[r] (bfloat16 rows of kdim values that other blocks wrote before the last barrier).
@@ -235,69 +271,96 @@ __device__ __forceinline__ void mma_16816_regs(float (&c)[4], uint32_t a0, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// out[r, n] (+)= sum_k stage[r, k] * W[n, k] for this block's tiles of 8 features. SUBS = 2: W holds N gate rows and,
-// `N` rows further, N up rows; the output is silu(gate) * up.
+// out[r, n] (+)= scale_r * sum_k stage[r, k] * W[n, k] for this block's tiles of 8 features (scale_r = 1 / rms of row r
+// when the rows came through stage_scaled: eps > 0). SUBS = 2: W holds N gate rows and, `N` rows further, N up rows;
+// the output is silu(gate) * up. A block multiplies up to kDlMaxAcc tiles (a pass) before its warps' partial sums are
+// added, in warp order, through shared memory: one exchange per pass instead of one per tile. A warp keeps two
+// accumulators per tile, which halves the chain of dependent instructions.
 template <int SUBS>
-__device__ bool gemm_phase(const DlArgs& a, DlCtx& c, int N, int kdim, int mode, void* out, int ldo) {
+__device__ bool gemm_phase(const DlArgs& a, DlCtx& c, int N, int kdim, int mode, void* out, int ldo, float eps) {
+  constexpr int MAXT = kDlMaxAcc / SUBS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int B = a.B, AS = stage_stride(kdim);
   const int tiles = (N + 7) / 8, chunks = (kdim + kDlKC - 1) / kDlKC;
+  const int first = (c.cta - c.rot + c.nblocks) % c.nblocks;
+  const int mine = first < tiles ? (tiles - first + c.nblocks - 1) / c.nblocks : 0;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const unsigned char* xa = c.stage + (size_t)g * AS + t * 16;
   const unsigned char* xb = c.stage + (size_t)(g + 8) * AS + t * 16;
   const bool has_a = g < B, has_b = g + 8 < B;
-  for (int tile = (c.cta - c.rot + c.nblocks) % c.nblocks; tile < tiles; tile += c.nblocks) {
-    // the old stream values of this thread's output, asked for before the products
-    const int er = threadIdx.x >> 3, ec = threadIdx.x & 7, feat = tile * 8 + ec;
-    const bool writes = threadIdx.x < 128 && er < B && feat < N;
-    float old = 0.0f;
-    if (mode == kDlAddF32 && writes) old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)er * ldo + feat);
-    float acc[SUBS][4];
+  // thread (row er, feature ec of a tile) adds up and stores that output of every tile; 1 / rms of its row once
+  const int er = threadIdx.x >> 3, ec = threadIdx.x & 7;
+  const bool stores = threadIdx.x < 128 && er < B;
+  const float scale = (stores && eps > 0.0f) ? row_scale(a, c, er, eps) : 1.0f;
+  for (int t0 = 0; t0 < mine; t0 += MAXT) {
+    const int nt = min(MAXT, mine - t0);
+    // Tile after tile (a plain loop: the code stays small enough for the instruction cache): the products of a tile,
+    // then this warp's partial sums of it into shared memory, rows that exist only. No warp waits for another here.
+#pragma unroll 1
+    for (int ti = 0; ti < nt; ++ti) {
+      float acc[SUBS][2][4];
 #pragma unroll
-    for (int s = 0; s < SUBS; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.0f;
+      for (int sb = 0; sb < SUBS; ++sb)
 #pragma unroll
-    for (int s = 0; s < SUBS; ++s) {
-      for (int ch = 0; ch < chunks; ++ch) {
-        const unsigned int fill = c.fill++;
-        if (!slot_wait(a, c, fill)) return false;
-        const int kc = min(kDlKC, kdim - ch * kDlKC);
-        const unsigned char* wrow = c.ring + (size_t)(fill % c.n_slots) * kDlSlot + g * kDlRowStride + t * 16;
-        for (int kb = warp; kb < kc / 32; kb += kDlConsumerWarps) {
-          const uint4 w = *reinterpret_cast<const uint4*>(wrow + kb * 64);
-          const size_t ko = ((size_t)ch * kDlKC + kb * 32) * 2;
-          const uint4 x0 = has_a ? *reinterpret_cast<const uint4*>(xa + ko) : zero;
-          const uint4 x1 = has_b ? *reinterpret_cast<const uint4*>(xb + ko) : zero;
-          mma_16816_regs(acc[s], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
-          mma_16816_regs(acc[s], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+        for (int e = 0; e < 4; ++e) acc[sb][0][e] = acc[sb][1][e] = 0.0f;
+#pragma unroll
+      for (int sb = 0; sb < SUBS; ++sb) {
+#pragma unroll 1
+        for (int ch = 0; ch < chunks; ++ch) {
+          const unsigned int fill = c.fill++;
+          if (!slot_wait(a, c, fill)) return false;
+          const int kc = min(kDlKC, kdim - ch * kDlKC);
+          const unsigned char* wrow = c.ring + (size_t)(fill % c.n_slots) * kDlSlot + g * kDlRowStride + t * 16;
+#pragma unroll 2
+          for (int kb = warp; kb < kc / 32; kb += kDlConsumerWarps) {
+            const uint4 w = *reinterpret_cast<const uint4*>(wrow + kb * 64);
+            const size_t ko = ((size_t)ch * kDlKC + kb * 32) * 2;
+            const uint4 x0 = has_a ? *reinterpret_cast<const uint4*>(xa + ko) : zero;
+            const uint4 x1 = has_b ? *reinterpret_cast<const uint4*>(xb + ko) : zero;
+            mma_16816_regs(acc[sb][0], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
+            mma_16816_regs(acc[sb][1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+          }
+          slot_release(c, fill);
         }
-        slot_release(c, fill);
       }
-    }
-    // the eight warps' partial sums, added in warp order
-    float* red = c.red + (size_t)c.red_buf * (2 * kDlConsumerWarps * 16 * 9);
-    c.red_buf ^= 1;
 #pragma unroll
-    for (int s = 0; s < SUBS; ++s) {
-      float* rw = red + ((size_t)s * kDlConsumerWarps + warp) * (16 * 9);
-      rw[g * 9 + 2 * t] = acc[s][0];
-      rw[g * 9 + 2 * t + 1] = acc[s][1];
-      rw[(g + 8) * 9 + 2 * t] = acc[s][2];
-      rw[(g + 8) * 9 + 2 * t + 1] = acc[s][3];
+      for (int sb = 0; sb < SUBS; ++sb) {
+        float* rw = c.red + ((size_t)(ti * SUBS + sb) * kDlConsumerWarps + warp) * (B * 9);
+        if (has_a) {
+          rw[g * 9 + 2 * t] = acc[sb][0][0] + acc[sb][1][0];
+          rw[g * 9 + 2 * t + 1] = acc[sb][0][1] + acc[sb][1][1];
+        }
+        if (has_b) {
+          rw[(g + 8) * 9 + 2 * t] = acc[sb][0][2] + acc[sb][1][2];
+          rw[(g + 8) * 9 + 2 * t + 1] = acc[sb][0][3] + acc[sb][1][3];
+        }
+      }
     }
     dl_bar();
-    if (writes) {
-      float v = 0.0f;
+    if (stores) {
+#pragma unroll 1
+      for (int ti = 0; ti < nt; ++ti) {
+        const int feat = (first + (t0 + ti) * c.nblocks) * 8 + ec;
+        if (feat >= N) continue;
+        const float* rr = c.red + (size_t)(ti * SUBS) * kDlConsumerWarps * (B * 9) + er * 9 + ec;
+        float v = 0.0f;
 #pragma unroll
-      for (int w8 = 0; w8 < kDlConsumerWarps; ++w8) v += red[(size_t)w8 * (16 * 9) + er * 9 + ec];
-      if (SUBS == 2) {
-        float u = 0.0f;
+        for (int w8 = 0; w8 < kDlConsumerWarps; ++w8) v += rr[(size_t)w8 * (B * 9)];
+        v *= scale;
+        if (SUBS == 2) {
+          float u = 0.0f;
 #pragma unroll
-        for (int w8 = 0; w8 < kDlConsumerWarps; ++w8) u += red[((size_t)kDlConsumerWarps + w8) * (16 * 9) + er * 9 + ec];
-        v = (v / (1.0f + expf(-v))) * u;
+          for (int w8 = 0; w8 < kDlConsumerWarps; ++w8) u += rr[(size_t)(kDlConsumerWarps + w8) * (B * 9)];
+          u *= scale;
+          v = (v / (1.0f + expf(-v))) * u;
+        }
+        // Adding into the stream: every element of it belongs to exactly one thread of the grid in a phase, so the one
+        // addition can be left to the memory system (a reduction that returns nothing) and nothing waits for the old value.
+        if (mode == kDlAddF32) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(out) + (size_t)er * ldo + feat), "f"(v) : "memory");
+        else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)er * ldo + feat] = __float2bfloat16_rn(v);
       }
-      if (mode == kDlAddF32) reinterpret_cast<float*>(out)[(size_t)er * ldo + feat] = old + v;
-      else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)er * ldo + feat] = __float2bfloat16_rn(v);
     }
+    dl_bar();        // the partial sums are rewritten by the next pass or phase
   }
   c.rot = (c.rot + tiles) % c.nblocks;
   return true;
@@ -401,7 +464,7 @@ __device__ bool attention_phase(const DlArgs& a, DlCtx& c, const DlLayer& L) {
   for (int q = lo; q < hi; ++u) {
     const int seg_end = min(hi, pre[u + 1]);
     const int seq = u / Kh, kh = u % Kh;
-    const int pos = a.past[seq];
+    const int pos = c.past[seq];
     const int key_lo = L.window > 0 ? max(0, pos - L.window + 1) : 0;
     const int page_lo = key_lo / 64, page_hi = pos / 64;
     const int first_page = page_lo + (q - pre[u]), n_pg = seg_end - q;
@@ -474,15 +537,17 @@ __device__ bool attention_phase(const DlArgs& a, DlCtx& c, const DlLayer& L) {
       uint32_t pf[2] = {0u, 0u};
       float alpha[2] = {1.0f, 1.0f};
       if (live) {
-        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const uint32_t kS = smem_u32(slot_k);
 #pragma unroll
         for (int kb2 = 0; kb2 < HD / 32; ++kb2) {
           uint32_t kf[4];
           ldmatrix_x4(kf, kS + tma_swz(warp * 8 + (lane & 7), kb2 * 32 + ((lane >> 3) << 3)));
           mma_bf16(s, qf[2 * kb2], kf[0], kf[1]);
-          mma_bf16(s, qf[2 * kb2 + 1], kf[2], kf[3]);
+          mma_bf16(s2, qf[2 * kb2 + 1], kf[2], kf[3]);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] += s2[e];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + 2 * t4 + (e & 1);
@@ -642,32 +707,32 @@ __device__ bool produce_gemm(const DlArgs& a, DlCtx& c, DlProducer& p, const __n
   return true;
 }
 
+// The place of page q of the flattened list of plan `plan` in cache group `group`: (physical page * kv heads + kv head),
+// i.e. the page's first row in the pool divided by 64.
+__device__ __forceinline__ int page_place(const DlArgs& a, const int* pre, const int* past, int plan, int group, int q, int n_units) {
+  const int Kh = a.plan_kv_heads[plan], W = a.plan_window[plan];
+  int left = 0, right = n_units - 1;
+  while (left < right) {          // the unit that holds page q: the last u with pre[u] <= q
+    const int mid = (left + right + 1) >> 1;
+    if (pre[mid] <= q) left = mid; else right = mid - 1;
+  }
+  const int seq = left / Kh, kh = left % Kh, pos = past[seq];
+  const int page = (W > 0 ? max(0, pos - W + 1) : 0) / 64 + (q - pre[left]);
+  return a.tables[group][(size_t)seq * a.table_stride[group] + page] * Kh + kh;
+}
+
 template <int HD>
-__device__ bool produce_attention(const DlArgs& a, DlCtx& c, DlProducer& p, const DlLayer& L, const CUtensorMap* map) {
-  const int Kh = L.kv_heads, n_units = a.B * Kh;
+__device__ bool produce_attention(const DlArgs& a, DlCtx& c, DlProducer& p, const DlLayer& L, const CUtensorMap* map, const int* places) {
+  const int n_units = a.B * L.kv_heads;
   const int* pre = c.pre + L.plan * (kDlMaxUnits + 1);
   const int P = pre[n_units];
   const int nb = min(c.nblocks, P);
   if (c.cta >= nb) return true;
   const int lo = (int)((long long)c.cta * P / nb), hi = (int)((long long)(c.cta + 1) * P / nb);
-  int u = 0;
-  {
-    int left = 0, right = n_units - 1;
-    while (left < right) {
-      const int mid = (left + right + 1) >> 1;
-      if (pre[mid] <= lo) left = mid; else right = mid - 1;
-    }
-    u = left;
-  }
-  const int stride = a.table_stride[L.group];
   for (int q = lo; q < hi; ++q) {
-    while (q >= pre[u + 1]) ++u;
-    const int seq = u / Kh, kh = u % Kh;
-    const int pos = a.past[seq];
-    const int key_lo = L.window > 0 ? max(0, pos - L.window + 1) : 0;
-    const int page = key_lo / 64 + (q - pre[u]);
-    const int phys = a.tables[L.group][(size_t)seq * stride + page];
-    const long long row = ((long long)phys * Kh + kh) * 64;
+    // looked up ahead of time by the whole warp (fill_places); beyond that list, here
+    const int place = q - lo < kDlMaxRun ? places[q - lo] : page_place(a, pre, c.past, L.plan, L.group, q, n_units);
+    const long long row = (long long)place * 64;
     for (int kv = 0; kv < 2; ++kv) {
       uint32_t bar;
       const uint32_t dst = produce_slot(a, c, p, (uint32_t)(64 * HD * 2), bar);
@@ -687,7 +752,10 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t bars[2 * kDlMaxSlots];
+  __shared__ __align__(16) DlLayer layer_now[2];                  // this layer's description and the next one's
   __shared__ int pre[kDlMaxPlans * (kDlMaxUnits + 1)];
+  __shared__ int places[kDlMaxCombos * kDlMaxRun];                // where the pages of this block's runs lie
+  __shared__ int past[16];
   __shared__ float ss[16 * 8];
   __shared__ int flag[2];
 
@@ -695,21 +763,23 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
   c.ring = smem;
   c.stage = smem + (size_t)a.n_slots * kDlSlot;
   c.red = reinterpret_cast<float*>(c.stage + a.stage_bytes);
-  c.sq = reinterpret_cast<unsigned char*>(c.red + 2 * 2 * kDlConsumerWarps * 16 * 9);
+  c.sq = reinterpret_cast<unsigned char*>(c.red + (size_t)kDlMaxAcc * kDlConsumerWarps * a.B * 9);
   c.ss = ss;
   c.pre = pre;
+  c.past = past;
   c.flag = flag;
   c.full0 = smem_addr(bars);
   c.empty0 = c.full0 + 8 * kDlMaxSlots;
   c.fill = 0;
   c.epoch = 0;
   c.rot = 0;
-  c.red_buf = 0;
+  c.waited = 0;
+  c.norm_parts = 1;
   c.cta = blockIdx.x;
   c.nblocks = gridDim.x;
   c.n_slots = a.n_slots;
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.n_slots; ++s) {
       mbar_init(c.full0 + 8 * s, 1);
@@ -718,6 +788,11 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     flag[0] = 0;
     flag[1] = 0;
+  }
+  if (threadIdx.x < 16) past[threadIdx.x] = threadIdx.x < a.B ? a.past[threadIdx.x] : 0;
+  if (warp == 1) {        // the first layer's description
+    const unsigned long long* src = reinterpret_cast<const unsigned long long*>(a.layers);
+    for (int i = lane; i < (int)(sizeof(DlLayer) / 8); i += 32) reinterpret_cast<unsigned long long*>(&layer_now[0])[i] = src[i];
   }
   // where each (sequence, kv head) unit's pages begin in the flattened list, per plan
   for (int i = threadIdx.x; i < a.n_plans * (kDlMaxUnits + 1); i += kDlThreads) {
@@ -737,8 +812,23 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
   __syncthreads();
 
   if (warp == kDlConsumerWarps) {
-    // ---- the producer: one lane walks this block's share of the whole step's stream ----
-    if (threadIdx.x == kDlConsumers) {
+    // ---- the producer ----
+    // All lanes first look up where this block's pages lie, for each (plan, cache group) pair among the layers: the
+    // block table is read through two dependent loads per page, which the one lane that issues the copies would
+    // otherwise wait for page by page.
+    for (int cb = 0; cb < a.n_combos; ++cb) {
+      const int plan = a.combo_plan[cb], group = a.combo_group[cb];
+      const int n_units = a.B * a.plan_kv_heads[plan];
+      const int* pr = pre + plan * (kDlMaxUnits + 1);
+      const int P = pr[n_units], nb = min(c.nblocks, P);
+      if (c.cta >= nb) continue;
+      const int lo = (int)((long long)c.cta * P / nb), hi = (int)((long long)(c.cta + 1) * P / nb);
+      for (int q = lo + lane; q < hi && q - lo < kDlMaxRun; q += 32)
+        places[cb * kDlMaxRun + q - lo] = page_place(a, pr, past, plan, group, q, n_units);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      // one lane walks this block's share of the whole step's stream
       DlProducer p;
       p.ring = smem_addr(c.ring);
       p.full0 = c.full0;
@@ -750,7 +840,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         const DlLayer L = a.layers[li];
         const int n_qkv = (L.heads + 2 * L.kv_heads) * HD;
         ok = produce_gemm(a, c, p, L.w_qkv, n_qkv, a.d, 1);
-        ok = ok && produce_attention<HD>(a, c, p, L, L.group == 0 ? &map0 : &map1);
+        ok = ok && produce_attention<HD>(a, c, p, L, L.group == 0 ? &map0 : &map1, places + L.combo * kDlMaxRun);
         ok = ok && produce_gemm(a, c, p, L.w_o, a.d, L.heads * HD, 1);
         ok = ok && produce_gemm(a, c, p, L.w_gu, L.inter, a.d, 2);
         ok = ok && produce_gemm(a, c, p, L.w_down, a.d, L.inter, 1);
@@ -766,38 +856,49 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     // ---- the consumers ----
     bool ok = true;
     for (int li = 0; li < a.n_layers && ok; ++li) {
-      const DlLayer L = a.layers[li];
+      const DlLayer& L = layer_now[li & 1];
+      // the next layer's description comes in meanwhile; the barriers of this layer stand between this write and its use
+      if (warp == 1 && li + 1 < a.n_layers) {
+        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(a.layers + li + 1);
+        for (int i = lane; i < (int)(sizeof(DlLayer) / 8); i += 32)
+          reinterpret_cast<unsigned long long*>(&layer_now[(li + 1) & 1])[i] = src[i];
+      }
       const int n_qkv = (L.heads + 2 * L.kv_heads) * HD;
       dl_stamp(a, li, 0);
-      stage_norm(a, c, L.norm1, L.eps1);
+      stage_scaled(a, c, L.norm1);
       dl_stamp(a, li, 1);
-      ok = gemm_phase<1>(a, c, n_qkv, a.d, kDlStoreBf16, a.qkv, n_qkv);
+      ok = gemm_phase<1>(a, c, n_qkv, a.d, kDlStoreBf16, a.qkv, n_qkv, L.eps1);
       dl_stamp(a, li, 2);
+      dl_stamp_wait(a, c, li, 15);
       ok = ok && grid_barrier(a, c);
       dl_stamp(a, li, 3);
       ok = ok && attention_phase<HD>(a, c, L);
       dl_stamp(a, li, 4);
+      dl_stamp_wait(a, c, li, 16);
       ok = ok && grid_barrier(a, c);
       dl_stamp(a, li, 5);
       if (!ok) break;
       stage_copy(a, c, a.y, L.heads * HD);
       dl_stamp(a, li, 6);
-      ok = gemm_phase<1>(a, c, a.d, L.heads * HD, kDlAddF32, a.x, a.d);
+      ok = gemm_phase<1>(a, c, a.d, L.heads * HD, kDlAddF32, a.x, a.d, 0.0f);
       dl_stamp(a, li, 7);
+      dl_stamp_wait(a, c, li, 17);
       ok = ok && grid_barrier(a, c);
       dl_stamp(a, li, 8);
       if (!ok) break;
-      stage_norm(a, c, L.norm2, L.eps2);
+      stage_scaled(a, c, L.norm2);
       dl_stamp(a, li, 9);
-      ok = gemm_phase<2>(a, c, L.inter, a.d, kDlSwiglu, a.act, L.inter);
+      ok = gemm_phase<2>(a, c, L.inter, a.d, kDlSwiglu, a.act, L.inter, L.eps2);
       dl_stamp(a, li, 10);
+      dl_stamp_wait(a, c, li, 18);
       ok = ok && grid_barrier(a, c);
       dl_stamp(a, li, 11);
       if (!ok) break;
       stage_copy(a, c, a.act, L.inter);
       dl_stamp(a, li, 12);
-      ok = gemm_phase<1>(a, c, a.d, L.inter, kDlAddF32, a.x, a.d);
+      ok = gemm_phase<1>(a, c, a.d, L.inter, kDlAddF32, a.x, a.d, 0.0f);
       dl_stamp(a, li, 13);
+      dl_stamp_wait(a, c, li, 19);
       ok = ok && grid_barrier(a, c);
       dl_stamp(a, li, 14);
     }
@@ -828,7 +929,8 @@ static int encode_pool_map(CUtensorMap* map, const void* base, long long rows, i
   return 0;
 }
 
-constexpr int kDlFixedSmem = 2 * 2 * kDlConsumerWarps * 16 * 9 * 4 + 16 * 128 * 2 + 1024;      // partial sums, query tile, alignment
+constexpr int kDlFixedSmem = 16 * 128 * 2 + 1024;      // query tile, alignment
+static int dl_red_bytes(int rows) { return kDlMaxAcc * kDlConsumerWarps * rows * 9 * 4; }   // the warps' partial sums of a pass
 
 template <int HD>
 static int launch_decode_layers(const DlHost& h, const CUtensorMap& m0, const CUtensorMap& m1, int smem, cudaStream_t s) {
@@ -871,11 +973,11 @@ extern "C" int slb_decode_layers_stage_bytes(int rows, int kmax, int head_dim) {
   return (need + 1023) & ~1023;
 }
 
-extern "C" int slb_decode_layers_slots(int stage_bytes) {
+extern "C" int slb_decode_layers_slots(int stage_bytes, int rows) {
   int dev = 0, most = 0;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&most, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-  const int room = most - 12 * 1024 - kDlFixedSmem - stage_bytes;      // 12 KB: the kernel's static arrays and a margin
+  const int room = most - 14 * 1024 - kDlFixedSmem - dl_red_bytes(rows) - stage_bytes;      // 14 KB: the kernel's static arrays and a margin
   const int n = room / kDlSlot;
   return n > kDlMaxSlots ? kDlMaxSlots : n;
 }
@@ -888,8 +990,13 @@ extern "C" int slb_decode_layers(const DlHost* host, void* stream) {
   SLB_REQUIRE(a.B >= 1 && a.B <= 16, "decode_layers: 1 to 16 sequences, got %d", a.B);
   SLB_REQUIRE(a.d >= 128 && a.d % 128 == 0, "decode_layers: the width must be a multiple of 128, got %d", a.d);
   SLB_REQUIRE(a.n_layers >= 1 && a.layers != nullptr, "decode_layers: no layers");
-  SLB_REQUIRE(a.n_plans >= 1 && a.n_plans <= kDlMaxPlans && h.n_groups >= 1 && h.n_groups <= 2,
-              "decode_layers: %d page plans (at most %d), %d cache groups (at most 2)", a.n_plans, kDlMaxPlans, h.n_groups);
+  SLB_REQUIRE(a.n_plans >= 1 && a.n_plans <= kDlMaxPlans && h.n_groups >= 1 && h.n_groups <= 2 && a.n_combos >= 1 &&
+              a.n_combos <= kDlMaxCombos,
+              "decode_layers: %d page plans (at most %d), %d cache groups (at most 2), %d pairs of them (at most %d)", a.n_plans,
+              kDlMaxPlans, h.n_groups, a.n_combos, kDlMaxCombos);
+  for (int cb = 0; cb < a.n_combos; ++cb)
+    SLB_REQUIRE(a.combo_plan[cb] >= 0 && a.combo_plan[cb] < a.n_plans && a.combo_group[cb] >= 0 && a.combo_group[cb] < h.n_groups,
+                "decode_layers: pair %d names plan %d, group %d", cb, a.combo_plan[cb], a.combo_group[cb]);
   for (int p = 0; p < a.n_plans; ++p)
     SLB_REQUIRE(a.plan_kv_heads[p] >= 1 && a.B * a.plan_kv_heads[p] <= kDlMaxUnits && a.plan_window[p] >= 0,
                 "decode_layers: %d sequences x %d kv heads are more than %d units", a.B, a.plan_kv_heads[p], kDlMaxUnits);
@@ -905,7 +1012,7 @@ extern "C" int slb_decode_layers(const DlHost* host, void* stream) {
   if (rc) return rc;
   rc = encode_pool_map(&m1, h.pool_base[h.n_groups > 1 ? 1 : 0], h.pool_rows[h.n_groups > 1 ? 1 : 0], h.head_dim);
   if (rc) return rc;
-  const int smem = a.n_slots * kDlSlot + a.stage_bytes + kDlFixedSmem;
+  const int smem = a.n_slots * kDlSlot + a.stage_bytes + dl_red_bytes(a.B) + kDlFixedSmem;
   return h.head_dim == 64 ? launch_decode_layers<64>(h, m0, m1, smem, (cudaStream_t)stream)
                           : launch_decode_layers<128>(h, m0, m1, smem, (cudaStream_t)stream);
 }

@@ -445,7 +445,7 @@ def gemm_tc_check(device) -> None:
 
 # ---------------------------------------------------------------- the persistent single-token kernel ----
 _VP, _LL, _CI, _CF = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
-DL_MAX_PLANS, DL_MAX_ROWS, DL_MAX_UNITS, DL_MAX_GROUP = 4, 16, 256, 8
+DL_MAX_PLANS, DL_MAX_ROWS, DL_MAX_UNITS, DL_MAX_GROUP, DL_MAX_COMBOS = 4, 16, 256, 8, 4
 
 
 class _DlLayer(ctypes.Structure):          # mirrors DlLayer in csrc/decode_layers.cu
@@ -453,14 +453,15 @@ class _DlLayer(ctypes.Structure):          # mirrors DlLayer in csrc/decode_laye
                                    "sin_table", "k_pool", "v_pool")] + \
                [("k_row0", _LL), ("v_row0", _LL), ("eps1", _CF), ("eps2", _CF), ("qk_eps", _CF), ("scale_log2", _CF),
                 ("heads", _CI), ("kv_heads", _CI), ("inter", _CI), ("window", _CI), ("group", _CI), ("plan", _CI),
-                ("pad0", _CI), ("pad1", _CI)]
+                ("combo", _CI), ("pad1", _CI)]
 
 
 class _DlArgs(ctypes.Structure):           # mirrors DlArgs
     _fields_ = [(n, _VP) for n in ("layers", "x", "qkv", "y", "act", "parts", "tickets", "barrier", "status", "past", "trace")] + \
                [("tables", _VP * 2), ("table_stride", _CI * 2), ("plan_window", _CI * DL_MAX_PLANS),
-                ("plan_kv_heads", _CI * DL_MAX_PLANS), ("n_plans", _CI), ("n_layers", _CI), ("B", _CI), ("d", _CI),
-                ("n_slots", _CI), ("stage_bytes", _CI)]
+                ("plan_kv_heads", _CI * DL_MAX_PLANS), ("combo_plan", _CI * DL_MAX_COMBOS), ("combo_group", _CI * DL_MAX_COMBOS),
+                ("n_plans", _CI), ("n_combos", _CI), ("n_layers", _CI), ("B", _CI), ("d", _CI), ("n_slots", _CI),
+                ("stage_bytes", _CI), ("pad", _CI)]
 
 
 class _DlHost(ctypes.Structure):           # mirrors DlHost
@@ -471,10 +472,10 @@ class DecodeProgram:
     """A run of layers prepared for ``decode_layers``: the layers' descriptions in device memory and what is the same
     for every launch. Built by ``decode_program`` from what the layers' parts offer (``Part.fused_decode``)."""
 
-    def __init__(self, layers_dev, n_layers, head_dim, hidden, kmax, max_qkv, max_heads, max_inter, plans, groups, keep):
+    def __init__(self, layers_dev, n_layers, head_dim, hidden, kmax, max_qkv, max_heads, max_inter, plans, groups, combos, keep):
         self.layers_dev, self.n_layers, self.head_dim, self.hidden, self.kmax = layers_dev, n_layers, head_dim, hidden, kmax
         self.max_qkv, self.max_heads, self.max_inter = max_qkv, max_heads, max_inter
-        self.plans, self.groups, self.keep = plans, groups, keep
+        self.plans, self.groups, self.combos, self.keep = plans, groups, combos, keep
         device = layers_dev.device
         self.tickets = torch.zeros(DL_MAX_UNITS, dtype=torch.int32, device=device)
         self.barrier = torch.zeros(4, dtype=torch.int32, device=device)
@@ -487,7 +488,7 @@ class DecodeProgram:
             dll.slb_decode_layers_stage_bytes.restype = ctypes.c_int
             dll.slb_decode_layers_slots.restype = ctypes.c_int
             stage = int(dll.slb_decode_layers_stage_bytes(int(rows), int(self.kmax), int(self.head_dim)))
-            self._slots[rows] = (int(dll.slb_decode_layers_slots(stage)), stage)
+            self._slots[rows] = (int(dll.slb_decode_layers_slots(stage, int(rows))), stage)
         return self._slots[rows]
 
 
@@ -500,7 +501,7 @@ def decode_program(shares: list, views: list, pools: list) -> DecodeProgram | No
         return None
     hd = shares[0]["mixer"]["head_dim"]
     d = shares[0]["mixer"]["hidden"]
-    group_ids, plans, keep = [], [], []
+    group_ids, plans, combos, keep = [], [], [], []
     arr = (_DlLayer * len(shares))()
     kmax = max_qkv = max_heads = max_inter = 0
     for i, (sh, view) in enumerate(zip(shares, views)):
@@ -512,7 +513,10 @@ def decode_program(shares: list, views: list, pools: list) -> DecodeProgram | No
         plan = (int(m["window"]), int(m["kv_heads"]))
         if plan not in plans:
             plans.append(plan)
-        if len(group_ids) > 2 or len(plans) > DL_MAX_PLANS:
+        combo = (plans.index(plan), group_ids.index(view.group))
+        if combo not in combos:
+            combos.append(combo)
+        if len(group_ids) > 2 or len(plans) > DL_MAX_PLANS or len(combos) > DL_MAX_COMBOS:
             return None
         pool = pools[view.group]
         L = arr[i]
@@ -534,7 +538,7 @@ def decode_program(shares: list, views: list, pools: list) -> DecodeProgram | No
         L.eps1, L.eps2, L.qk_eps = float(sh["norm1"]["eps"]), float(sh["norm2"]["eps"]), float(m["qk_eps"])
         L.scale_log2 = float(m["scale"]) * 1.4426950408889634
         L.heads, L.kv_heads, L.inter, L.window = int(m["heads"]), int(m["kv_heads"]), int(f["inter"]), int(m["window"])
-        L.group, L.plan = group_ids.index(view.group), plans.index(plan)
+        L.group, L.plan, L.combo = group_ids.index(view.group), plans.index(plan), combos.index(combo)
         n_qkv = (L.heads + 2 * L.kv_heads) * hd
         _need(tuple(m["w_qkv"].shape) == (n_qkv, d) and tuple(m["w_o"].shape) == (d, L.heads * hd) and
               tuple(f["w_gu"].shape) == (2 * L.inter, d) and tuple(f["w_down"].shape) == (d, L.inter),
@@ -545,7 +549,8 @@ def decode_program(shares: list, views: list, pools: list) -> DecodeProgram | No
     raw = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(device)
     groups = [(pools[g], pools[g].numel() // hd) for g in group_ids]
     keep.extend(p for p, _ in groups)
-    return DecodeProgram(raw, len(shares), hd, d, kmax, max_qkv, max_heads, max_inter, plans, [(gid, *g) for gid, g in zip(group_ids, groups)], keep)
+    return DecodeProgram(raw, len(shares), hd, d, kmax, max_qkv, max_heads, max_inter, plans,
+                         [(gid, *g) for gid, g in zip(group_ids, groups)], combos, keep)
 
 
 def decode_layers_scratch_floats(prog: DecodeProgram, rows: int, blocks: int) -> int:
@@ -557,8 +562,8 @@ def decode_layers(prog: DecodeProgram, x: torch.Tensor, past: torch.Tensor, tabl
     """Run the program's layers on the float32 stream ``x [B, hidden]`` of a step in which each of the B sequences
     brings one token: ``past [B]`` their positions, ``tables`` the step's block table of every cache group
     (indexed as the cache indexes its groups). ``qkv``, ``y``, ``act`` (bfloat16) and ``parts`` (float32) are scratch.
-    ``trace``: None, or an int64 tensor [blocks, layers, 16] that receives every block's nanosecond stamps at the phase
-    boundaries of every layer (a diagnostic: where the step's time goes)."""
+    ``trace``: None, or an int64 tensor [blocks, layers, 24] that receives every block's nanosecond stamps at the phase
+    boundaries of every layer (entries 0-14) and the clock cycles each phase waited for its data (15-19): a diagnostic."""
     _cuda(x, past, qkv, y, act, parts)
     B, d = x.shape
     _need(x.dtype == torch.float32 and d == prog.hidden and 1 <= B <= DL_MAX_ROWS, "decode_layers: x is float32 [1..16, hidden]")
@@ -573,7 +578,7 @@ def decode_layers(prog: DecodeProgram, x: torch.Tensor, past: torch.Tensor, tabl
     a.layers, a.x, a.qkv, a.y, a.act, a.parts = prog.layers_dev.data_ptr(), x.data_ptr(), qkv.data_ptr(), y.data_ptr(), act.data_ptr(), parts.data_ptr()
     a.tickets, a.barrier, a.status, a.past = prog.tickets.data_ptr(), prog.barrier.data_ptr(), _tc_status(x.device).data_ptr(), past.data_ptr()
     if trace is not None:
-        _need(trace.is_cuda and trace.dtype == torch.int64 and trace.numel() >= blocks * prog.n_layers * 16, "decode_layers: trace is int64 [blocks, layers, 16]")
+        _need(trace.is_cuda and trace.dtype == torch.int64 and trace.numel() >= blocks * prog.n_layers * 24, "decode_layers: trace is int64 [blocks, layers, 24]")
     a.trace = _p(trace)
     for i, (gid, pool, rows) in enumerate(prog.groups):
         t = tables[gid]
@@ -582,7 +587,9 @@ def decode_layers(prog: DecodeProgram, x: torch.Tensor, past: torch.Tensor, tabl
         h.pool_base[i], h.pool_rows[i] = pool.data_ptr(), rows
     for i, (window, kvh) in enumerate(prog.plans):
         a.plan_window[i], a.plan_kv_heads[i] = window, kvh
-    a.n_plans, a.n_layers, a.B, a.d, a.n_slots, a.stage_bytes = len(prog.plans), prog.n_layers, B, d, n_slots, stage
+    for i, (plan, group) in enumerate(prog.combos):
+        a.combo_plan[i], a.combo_group[i] = plan, group
+    a.n_plans, a.n_combos, a.n_layers, a.B, a.d, a.n_slots, a.stage_bytes = len(prog.plans), len(prog.combos), prog.n_layers, B, d, n_slots, stage
     h.head_dim, h.n_groups = prog.head_dim, len(prog.groups)
     lib().call("slb_decode_layers", ctypes.addressof(h), stream if stream is not None else current_stream())
 

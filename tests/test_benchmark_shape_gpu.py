@@ -91,12 +91,16 @@ def test_last_32_tokens_one_by_one(dtype, folder, oracles):
     assert any(not isinstance(k[0], str) for k in eng.stepper._graphs)
 
 
-@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-def test_two_unequal_batches_of_eight_reuse_slots_and_pages(dtype, folder, oracles):
+@pytest.mark.parametrize("dtype", ["fp32", "bf16", "bf16-persistent"])
+def test_two_unequal_batches_of_eight_reuse_slots_and_pages(dtype, folder, oracles, monkeypatch):
     """Batch 8 is the benchmark's batch: in bfloat16 the decode attention then cuts every (sequence, kv head) into six
     slices over two page buffers, behind the few-rows q/k/v product with the norm fused in. The cache has room for
     one batch; the second gets the first one's slots and pages, still full of its keys. Shorter requests end earlier."""
     _, _, ref = oracles
+    if dtype == "bf16-persistent":          # the same through the persistent single-token kernel (csrc/decode_layers.cu)
+        from sleuth_b200.engine import model as model_mod
+        monkeypatch.setattr(model_mod, "DECODE_CHOICE", "fused")
+        dtype = "bf16"
     plans = [[(100, 6), (600, 9), (5, 9), (33, 1), (64, 4), (65, 9), (17, 2), (128, 5)],
              [(1, 9), (130, 3), (63, 9), (450, 7), (12, 9), (200, 2), (90, 9), (64, 6)]]
     pages = max(sum(-(-(p + d) // 64) for p, d in plan) for plan in plans)
