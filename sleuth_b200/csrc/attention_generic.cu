@@ -7,11 +7,14 @@
 // (attention.py:197-199); scores are (q . k) * scale, softmax and the weighted sum run in float32
 // (attention.py:200-206).
 //
-// One warp per (token, query head). Keys are taken 32 at a time, aligned to multiples of 32 positions: each lane
-// computes the whole dot product of its key (channels in ascending order), the warp keeps a running maximum and sum
-// (online softmax), then the lanes switch to channels for the weighted sum of values. The order of every addition
-// depends only on the token's own position and window, never on the batch or on how the sequence was cut into
-// steps, so in float32 the result is the same bit for bit under every schedule.
+// One block of eight warps per (token, query head). Keys are taken 32 at a time, aligned to multiples of 32 positions;
+// the groups of 32 go to the warps in turn (group i of the query's range to warp i % 8), so that a single token with
+// thousands of keys behind it still has eight warps at work. Within a group each lane computes the whole dot product
+// of its key (channels in ascending order), the warp keeps a running maximum and sum over its groups (online softmax),
+// then the lanes switch to channels for the weighted sum of values; at the end the eight warps' results are merged in
+// warp order. Which warp takes which keys, and so the order of every addition, depends only on the token's own
+// position and window, never on the batch or on how the sequence was cut into steps: in float32 the result is the
+// same bit for bit under every schedule.
 #include <math.h>
 
 #include "common.cuh"
@@ -71,15 +74,16 @@ template <> struct RowDot<__nv_bfloat16> {
   }
 };
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
 
 template <typename T, int PER_LANE>
-__global__ void attn_generic_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs a) {
   pdl_enter();
-  __shared__ float q_all[kAttnWarps][256];
+  __shared__ float qs[256];
+  __shared__ float part_acc[kAttnWarps][PER_LANE * 32];
+  __shared__ float part_m[kAttnWarps], part_l[kAttnWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kAttnWarps + warp;
-  if (item >= (long long)a.tokens * a.heads) return;
+  const long long item = blockIdx.x;
   const int t = (int)(item / a.heads), h = (int)(item - (long long)t * a.heads);
   const int hd = a.head_dim;
   const int kh = h / (a.heads / a.kv_heads);
@@ -87,10 +91,9 @@ __global__ void attn_generic_kernel(AttnArgs a) {
   const int* table = a.block_table + (size_t)a.tok_seq[t] * a.table_stride;
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
 
-  float* qs = q_all[warp];
   const T* qrow = (const T*)a.q + ((size_t)t * a.heads + h) * hd;
-  for (int c = lane; c < hd; c += 32) qs[c] = to_f32(qrow[c]);
-  __syncwarp();
+  for (int c = threadIdx.x; c < hd; c += kAttnWarps * 32) qs[c] = to_f32(qrow[c]);
+  __syncthreads();
 
   const T* kpool = (const T*)a.k_pool;
   const T* vpool = (const T*)a.v_pool;
@@ -100,7 +103,7 @@ __global__ void attn_generic_kernel(AttnArgs a) {
   for (int i = 0; i < PER_LANE; ++i) acc[i] = 0.0f;
   float m = -INFINITY, l = 0.0f;
 
-  for (int base = (lo / 32) * 32; base <= pos; base += 32) {
+  for (int base = (lo / 32) * 32 + 32 * warp; base <= pos; base += 32 * kAttnWarps) {
     const int j = base + lane;
     const bool valid = j >= lo && j <= pos;
     int row = 0;          // row of the pools: (page * K + kh) * 64 + j % 64
@@ -130,19 +133,31 @@ __global__ void attn_generic_kernel(AttnArgs a) {
     m = m_new;
   }
 
-  T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
-  const float inv = 1.0f / l;
+  // the warps' results (a warp that had no keys brings maximum -inf and sum 0), merged in warp order
 #pragma unroll
-  for (int i = 0; i < PER_LANE; ++i) {
-    const int c = lane + 32 * i;
-    if (c < hd) o[c] = from_f32<T>(acc[i] * inv);
+  for (int i = 0; i < PER_LANE; ++i) part_acc[warp][lane + 32 * i] = acc[i];
+  if (lane == 0) { part_m[warp] = m; part_l[warp] = l; }
+  __syncthreads();
+  float top = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, part_m[w]);
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kAttnWarps; ++w) total += part_l[w] * expf(part_m[w] - top);
+  T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
+  const float inv = 1.0f / total;
+  for (int c = threadIdx.x; c < hd; c += kAttnWarps * 32) {
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) v += part_acc[w][c] * expf(part_m[w] - top);
+    o[c] = from_f32<T>(v * inv);
   }
 }
 
 template <typename T>
 static int launch_attn_generic(const AttnArgs& a, cudaStream_t s) {
   const long long items = (long long)a.tokens * a.heads;
-  const long long blocks = (items + kAttnWarps - 1) / kAttnWarps;
+  const long long blocks = items;
   SLB_REQUIRE(blocks < (1ll << 31), "attention: too many rows (%lld)", items);
   const int per_lane = (a.head_dim + 31) / 32;
   const int threads = kAttnWarps * 32;

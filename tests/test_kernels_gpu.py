@@ -76,7 +76,8 @@ def test_embed_add_swiglu(dtype):
     torch.testing.assert_close(act.cpu().double(), gd * torch.sigmoid(gd) * ud, **tol(dtype))
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 33, 17), (5, 64, 96), (16, 503, 160), (17, 100, 1000), (130, 257, 75)])
+@pytest.mark.parametrize("M,N,K", [(1, 33, 17), (5, 64, 96), (16, 503, 160), (17, 100, 1000), (130, 257, 75), (96, 40, 36),
+                                   (300, 1024, 1024), (257, 130, 1030)])
 def test_gemm_f32_exact_and_row_independent(M, N, K):
     g = torch.Generator().manual_seed(M * N)
     a, w, bias = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
