@@ -409,8 +409,8 @@ def plain_learned_model(w, ids, HD=HD):
 
 # float32: summation order only. bfloat16 (head size 64, so that the tensor-core attention kernels serve the toy
 # parts' layers): weights rounded alike on both sides, activations rounded in the engine only; the logits of these
-# models are below 1 in magnitude and the largest difference seen on a B200 was 0.012.
-TOY_TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=2.5e-2, atol=2.5e-2)}
+# models are about 1 in magnitude and the largest difference seen on a B200 was 0.0032: the bound is twice that.
+TOY_TOL = {"fp32": dict(rtol=1e-4, atol=2e-5), "bf16": dict(rtol=0.0, atol=6.5e-3)}
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
@@ -487,3 +487,33 @@ def test_state_is_sized_by_sequences_not_by_pages(toy_registered):
     cache.close(slots)
     again = cache.open(12)
     assert float(cache.states[1][again].abs().sum()) == 0.0            # a slot taken again starts from a zeroed state
+
+
+def test_shared_cache_entry_with_every_kernel_starting_early(toy_registered, tmp_path):
+    """SLEUTH_B200_PDL=1 lets every kernel start while the one in front still runs. A layer that reads the cache entry
+    another layer application of the same step wrote must then not ask for its pages before that writer has finished:
+    single-token steps of the shared-cache toy model, in bfloat16 at head size 64 (the split-KV attention kernel with
+    its q/k/v prologue), against the plain implementation."""
+    import functools
+
+    import sleuth_b200 as sb
+    from sleuth_b200.kernels import ops
+    cfg = dict(architectures=["ToyForCausalLM"], model_type="toy", vocab_size=VOCAB, hidden_size=HID, variant="shared_kv",
+               head_dim=64)
+    folder = sb.write_random_model(tmp_path / "shared", cfg, seed=4, dtype=torch.float32)
+    _, w = plain.read_model(folder)
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    oracle = functools.partial(plain_shared_kv_model, HD=64)
+    dll = ops.lib().dll
+    before = dll.slb_get_pdl()
+    dll.slb_set_pdl(1)
+    try:
+        eng = sb.load(folder, dtype="bf16", max_seq_len=256, max_tokens=1024)
+        ids = np.random.default_rng(2).integers(0, VOCAB, size=150).tolist()
+        (slot,) = eng.open(1)
+        rows = [eng.step([(slot, ids[:100], (99,))]).cpu()]
+        rows += [eng.step([(slot, [t], (0,))]).cpu().clone() for t in ids[100:]]      # eager, then recorded and replayed
+        eng.close([slot])
+        check(torch.cat(rows), oracle(w, ids)[99:], TOY_TOL["bf16"], "toy parts bf16")
+    finally:
+        dll.slb_set_pdl(before)
