@@ -285,8 +285,10 @@ static int launch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
   }
 }
 
+// `features`: 0 lets the rule below choose how many output features (8, 16 or 32) a block takes; 8, 16 or 32 force it
+// (the caller has measured what this matrix likes: see parts/linear.py).
 template <bool NORM>
-static int dispatch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
+static int dispatch_skinny(const SkinnyArgs& a, int mode, int features, cudaStream_t s) {
   if (a.M > 32) {       // up to 64 rows: 8 or 16 features per block (the partial sums of 64 rows must fit shared memory)
     if (mode == kSwiglu || a.N < 4096) return launch_skinny<1, false, 4>(a, mode, s);
     return launch_skinny<2, false, 4>(a, mode, s);
@@ -295,6 +297,9 @@ static int dispatch_skinny(const SkinnyArgs& a, int mode, cudaStream_t s) {
     if (mode == kSwiglu || a.N < 4096) return launch_skinny<1, false, 2>(a, mode, s);
     return launch_skinny<2, false, 2>(a, mode, s);
   }
+  if (features == 8) return launch_skinny<1, NORM, 1>(a, mode, s);
+  if (features == 16) return launch_skinny<2, NORM, 1>(a, mode, s);
+  if (features == 32 && mode != kSwiglu) return launch_skinny<4, NORM, 1>(a, mode, s);
   // wide matrices: 16 or 32 features per block; narrow ones: 8, so that enough blocks exist to fill the GPU
   if (mode == kSwiglu) return a.N >= 4096 ? launch_skinny<2, NORM, 1>(a, mode, s) : launch_skinny<1, NORM, 1>(a, mode, s);
   if (a.N >= 32768) return launch_skinny<4, NORM, 1>(a, mode, s);
@@ -328,7 +333,7 @@ static int take_pages(SkinnyArgs& a, const NextPages* pages) {
 }
 
 extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
-                               const void* next, long long next_bytes, const NextPages* pages, void* stream) {
+                               const void* next, long long next_bytes, const NextPages* pages, int features, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 64, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
@@ -338,14 +343,15 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   if (int rc = take_pages(a, pages)) return rc;
-  return dispatch_skinny<false>(a, mode, (cudaStream_t)stream);
+  SLB_REQUIRE(features == 0 || features == 8 || features == 16 || features == 32, "gemm_skinny: features per block 0 (rule), 8, 16 or 32, got %d", features);
+  return dispatch_skinny<false>(a, mode, features, (cudaStream_t)stream);
 }
 
 // The same with the RMSNorm of the input fused in: X is the float32 stream [M, K], rows are normalised with
 // `gain` [K] and `eps` and rounded to bfloat16 on the way into the product.
 extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps, const void* W, void* C, int M, int N,
                                     int K, int ldc, int mode, const void* next, long long next_bytes,
-                                    const NextPages* pages, void* stream) {
+                                    const NextPages* pages, int features, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K) && M <= 16 && K <= kNormMaxK,
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel with the norm fused in takes (1 <= M <= 16, K a multiple of 32, at most %d)",
               M, N, K, kNormMaxK);
@@ -357,5 +363,6 @@ extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   if (int rc = take_pages(a, pages)) return rc;
-  return dispatch_skinny<true>(a, mode, (cudaStream_t)stream);
+  SLB_REQUIRE(features == 0 || features == 8 || features == 16 || features == 32, "gemm_skinny: features per block 0 (rule), 8, 16 or 32, got %d", features);
+  return dispatch_skinny<true>(a, mode, features, (cudaStream_t)stream);
 }

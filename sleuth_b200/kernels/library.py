@@ -140,8 +140,8 @@ _SIGNATURES = {
     "slb_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "slb_attention_tc": [P, P, P, P, P, P, P, P, I, I, I, L, L, I, I, I, I, F, P, P],
     "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, I, P, P, P, P, P, F, P, L, P],
-    "slb_gemm_skinny": [P, P, P, I, I, I, I, I, P, L, P, P],
-    "slb_gemm_skinny_norm": [P, P, F, P, P, I, I, I, I, I, P, L, P, P],
+    "slb_gemm_skinny": [P, P, P, I, I, I, I, I, P, L, P, I, P],
+    "slb_gemm_skinny_norm": [P, P, F, P, P, I, I, I, I, I, P, L, P, I, P],
     "slb_gemm_tc": [P, P, P, I, I, I, I, I, P, P],
     "slb_tc_wait_probe": [P, I, I, P],
     "slb_decode_layers": [P, P],

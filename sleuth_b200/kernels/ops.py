@@ -329,10 +329,11 @@ def _pages_arg(pages):
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None, next_read=None,
-                next_pages=None) -> None:
+                next_pages=None, features: int = 0) -> None:
     """out = x[M, K] @ w^T for M <= 16 (bfloat16 in, float32 accumulation). mode: "bf16" / "f32" store,
     "add" adds into a float32 ``out``, "swiglu" takes w = [gate rows; up rows] and stores silu(gate) * up.
-    ``next_read``: a weight tensor that the kernel after this one reads; the blocks ask the L2 cache for it."""
+    ``next_read``: a weight tensor that the kernel after this one reads; the blocks ask the L2 cache for it.
+    ``features``: output features a block takes (8, 16, 32; 0 = the launcher's rule)."""
     _cuda(x, w, out)
     M, K = x.shape
     N = out.shape[1]
@@ -340,11 +341,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, 
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny: output dtype")
     lib().call("slb_gemm_skinny", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode], _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
-               _pages_arg(next_pages), stream if stream is not None else current_stream())
+               _pages_arg(next_pages), int(features), stream if stream is not None else current_stream())
 
 
 def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor, mode: str,
-                     stream=None, next_read=None, next_pages=None) -> None:
+                     stream=None, next_read=None, next_pages=None, features: int = 0) -> None:
     """``gemm_skinny`` on rmsnorm(x; gain, eps): x is the float32 stream [M, K], normalised inside the kernel."""
     _cuda(x, gain, w, out)
     M, K = x.shape
@@ -354,7 +355,7 @@ def gemm_skinny_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.T
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny_norm: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny_norm: output dtype")
     lib().call("slb_gemm_skinny_norm", _p(x), _p(gain), float(eps), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode],
-               _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read), _pages_arg(next_pages),
+               _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read), _pages_arg(next_pages), int(features),
                stream if stream is not None else current_stream())
 
 

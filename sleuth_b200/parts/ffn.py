@@ -56,8 +56,10 @@ class GatedMLP(Part):
                     and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden, norm=True)):
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight)
             else:
-                ops.gemm_skinny(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream,
-                                self.down.weight)
+                hh = h.tensor() if isinstance(h, Normed) else h
+                f = linear.tuned_features("swiglu", T, self.spec.intermediate, self.spec.hidden,
+                                          lambda f: ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, features=f))
+                ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight, features=f)
         elif self.ctx.dtype == torch.bfloat16 and linear.use_tc(T, self.spec.intermediate, self.spec.hidden):
             ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
         else:

@@ -56,6 +56,56 @@ def use_skinny(M: int, N: int, K: int, norm: bool = False) -> bool:
 def use_tc(M: int, N: int, K: int) -> bool:
     return USE_TC and M >= TC_ROWS and ops.tc_supported(M, N, K)
 
+# How many output features a block of the weight-streaming kernel takes (8, 16 or 32) decides how many blocks there
+# are and how many fit an SM; which is fastest depends on the matrix (measured on a B200, 16 rows: a 2,560 x 9,728
+# down projection 19.1 us with 8, 15.9 us with 16; a gated 9,728 x 2,560 product 26.1 us with 16, 22.3 us with 8; the
+# 0.6B shapes are fastest with the launcher's own rule). So the first time a shape is met outside a graph recording,
+# the choices are timed on it (cold: the L2 cache is swept between runs) and the fastest is kept for the process.
+# The choice changes which block computes which feature, never a sum's order: results are the same bits for all.
+_FEATURES: dict = {}
+TUNE = os.environ.get("SLEUTH_B200_TUNE", "1") != "0"
+
+
+def _bucket(M: int) -> int:
+    return 1 if M <= 1 else (8 if M <= 8 else 16)
+
+
+def tuned_features(kind: str, M: int, N: int, K: int, launch) -> int:
+    """The features-per-block choice for this product; ``launch(features)`` runs it once on the current stream."""
+    if M > 16 or not TUNE:
+        return 0
+    key = (kind, _bucket(M), N, K)
+    best = _FEATURES.get(key)
+    if best is not None:
+        return best
+    if torch.cuda.is_current_stream_capturing():
+        return 0            # timed another time; the rule serves meanwhile
+    candidates = [0, 8, 16] + ([32] if kind != "swiglu" and N >= 1024 else [])
+    device = torch.cuda.current_device()
+    sweep = torch.empty(160 << 20, dtype=torch.uint8, device=f"cuda:{device}")        # larger than the L2 cache
+    times = {}
+    for f in candidates:
+        launch(f)
+        t = []
+        for _ in range(3):
+            sweep.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            launch(f)
+            b.record()
+            b.synchronize()
+            t.append(a.elapsed_time(b))
+        times[f] = min(t)
+    del sweep
+    # the rule's own choice stays unless something else is clearly faster (3 %: timing noise must not flip it)
+    best = 0
+    for f in candidates[1:]:
+        if times[f] < 0.97 * times[best]:
+            best = f
+    _FEATURES[key] = best
+    return best
+
+
 _MODE: dict = {}
 
 
@@ -105,8 +155,10 @@ class Linear:
                 want = out_dtype or (out.dtype if out is not None else self.dtype)
                 if out is None:
                     out = ws.take((M, self.out_features), want)
-                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, "f32" if want == torch.float32 else "bf16",
-                                     stream, next_read, next_pages)
+                mode = "f32" if want == torch.float32 else "bf16"
+                f = tuned_features("norm-" + mode, M, self.out_features, self.in_features,
+                                   lambda f: ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, mode, stream, features=f))
+                ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.weight, out, mode, stream, next_read, next_pages, features=f)
                 return out
             h = h.tensor()
         if self.dtype == torch.float32:
@@ -119,12 +171,18 @@ class Linear:
             return out
         if use_skinny(M, self.out_features, self.in_features):
             if into is not None:
-                ops.gemm_skinny(h, self.weight, into, "add", stream, next_read)
+                # (timing runs add into a scratch copy of the stream's shape, not into the stream)
+                f = tuned_features("add", M, self.out_features, self.in_features,
+                                   lambda f: ops.gemm_skinny(h, self.weight, torch.empty_like(into), "add", stream, features=f))
+                ops.gemm_skinny(h, self.weight, into, "add", stream, next_read, features=f)
                 return into
             want = out_dtype or (out.dtype if out is not None else self.dtype)
             if out is None:
                 out = ws.take((M, self.out_features), want)
-            ops.gemm_skinny(h, self.weight, out, "f32" if want == torch.float32 else "bf16", stream, next_read, next_pages)
+            mode = "f32" if want == torch.float32 else "bf16"
+            f = tuned_features(mode, M, self.out_features, self.in_features,
+                               lambda f: ops.gemm_skinny(h, self.weight, out, mode, stream, features=f))
+            ops.gemm_skinny(h, self.weight, out, mode, stream, next_read, next_pages, features=f)
             return out
         if use_tc(M, self.out_features, self.in_features):
             if into is not None:

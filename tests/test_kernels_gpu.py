@@ -95,6 +95,25 @@ def test_gemm_f32_exact_and_row_independent(M, N, K):
     torch.testing.assert_close(acc.cpu().double(), a.double() @ w.double().T + 2.0, rtol=1e-5, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,N,K,mode", [(1, 96, 256, "bf16"), (8, 2560, 1024, "add"), (16, 1000, 2560, "f32"), (5, 520, 384, "swiglu")])
+def test_gemm_skinny_features_per_block_change_no_bit(M, N, K, mode):
+    """How many output features a block takes (the launcher's rule, or 8, 16, 32 as the engine measures and chooses per
+    shape) decides which block computes which feature, never the order of a sum: every choice gives the same bits."""
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn((2 * N if mode == "swiglu" else N), K, generator=g) / 8).bfloat16().to(DEV)
+    base = torch.randn(M, N, generator=g).to(DEV)
+    outs = []
+    for f in (0, 8, 16) + (() if mode == "swiglu" else (32,)):
+        out = base.clone() if mode == "add" else torch.empty(M, N, device=DEV, dtype=torch.float32 if mode == "f32" else torch.bfloat16)
+        ops().gemm_skinny(x, w, out, mode, features=f)
+        outs.append(out.cpu())
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    if mode != "swiglu":
+        ref = x.float().cpu() @ w.float().cpu().T + (base.cpu() if mode == "add" else 0)
+        torch.testing.assert_close(outs[0].float(), ref, rtol=2e-2, atol=2e-2)
+
+
 # ------------------------------------------------------------------ cache layout helpers ----
 
 def make_cache(seq_lens, kv_heads, hd, dtype, gen, scramble=True):
