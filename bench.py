@@ -8,12 +8,17 @@ growing towards 4,096), timed on the device with CUDA events over exactly K deco
 warm-up steps; a step is one decode step of the whole batch including the choice of the next tokens.
 ``e2e`` is the same through the Python entry point (``Engine.generate``: host token lists in, host
 token lists out, one host-to-device copy of the step's tables and one device-to-host read of the
-chosen tokens per step). ``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1
-and 64; ``roofline`` relates the decode step to the memory bandwidth. Weights are random
-(N(0, 0.02)), token ids are seeded uniform: there is no dataset.
+chosen tokens per step). ``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step to the
+memory bandwidth. ``points`` holds decode at batch 1 (device-timed and through ``generate``) and 64, the
+4B-shaped configuration (16 ragged prompts of 64..2,048 tokens, 256 steps through ``generate``, greedy and
+at temperature 0.8) and the 8B-shaped one (untied, batch 64, 4,096-token prompts), each with its fraction
+of the memory bandwidth; ``fp32`` is the true 32-bit path at the 0.6B sizes (decode at batch 8, one
+2,048-token prompt) against its own rooflines. Weights are random (N(0, 0.02)), token ids are seeded
+uniform: there is no dataset. ``--skip-other-configs`` leaves the 32-bit block and the larger shapes out.
 
 ``--impl reference`` runs tbertha35/Sleuth itself (installed under baseline/_ref) on the same shapes
-through its own model, cache and sampling code.
+through its own model, cache and sampling code: its eager batch-8 loop after one untimed pass, best of
+three, and for batch 1 its own ``generate()`` with and without its CUDA-graph decoder.
 """
 
 from __future__ import annotations

@@ -113,13 +113,12 @@ struct DlCtx {
   const int* pre;                // [plans][kDlMaxUnits + 1] first page of each unit in the flattened list
   const int* past;               // [B] the sequences' positions, in shared memory
   int norm_parts;                // pieces each row's sum of squares came in
-  int* flag;                     // [0] ticket or barrier verdict (consumers), [1] block-wide abort
+  int* flag;                     // [0] a ticket, or whether a grid barrier was passed (consumers), [1] block-wide abort
   uint32_t full0, empty0;        // shared-memory addresses of the slots' barriers
   unsigned int fill;             // slots consumed (or produced) so far
   unsigned int epoch;            // grid barriers passed
   long long waited;              // clock cycles spent waiting for slots to fill (diagnostic, read by traced launches)
   int rot;                       // whose turn the next product's first tile is
-  int red_buf;
   int cta, nblocks, n_slots;
 };
 
