@@ -12,16 +12,20 @@
 //     that the tensor core reads, and issues S = Q K^T (M = 128, N = 64) into one of two score buffers in tensor
 //     memory, one page ahead of the softmax.
 //   * warp 1, one lane: the values. It asks TMA for the value pages and issues O += P V (M = 128, N = HD) as soon as
-//     the softmax has written P into shared memory; V is read in place as an N-major operand.
+//     the softmax has written P; P is read from tensor memory (the A operand), V in place from shared memory as an
+//     N-major operand.
 //   * warps 2 to 9: softmax, two threads per row (keys 0..31 and 32..63 of the page). They read their half of a score
 //     row from tensor memory, mask it, agree on the row's maximum through shared memory (the two warps of a row
-//     meet at a hardware barrier of their own, twice per page), write P as bfloat16 into
-//     shared memory, and when a row's maximum has grown by more than 2^8 since O was last scaled, rescale O in
-//     tensor memory (otherwise the old maximum keeps serving: exact, since numerator and denominator carry the
-//     same factor). At the end they add their sums, divide and store. Value rows of the last page that lie beyond
-//     the sequence are zeroed in shared memory before the product, so that leftovers of an earlier tenant of the
-//     page cannot reach the sum (0 * inf).
-// Two blocks fit on an SM (113 KB of shared memory and 256 columns of tensor memory each); while one waits for its
+//     meet at a hardware barrier of their own, once per page), write P as bfloat16 back into tensor memory, into
+//     the columns its scores came from (so P has two buffers as S has, and the softmax of a page does not wait for
+//     the product of the page before; a score buffer is written again only when the product that read its P is
+//     through), and when a row's maximum has grown by more than 2^8 since O was last scaled, wait for the last
+//     product and rescale O in tensor memory (otherwise the old maximum keeps serving: exact, since numerator and
+//     denominator carry the same factor). At the end they add their sums, divide, and store through shared memory
+//     so that a warp writes whole lines. Value rows of the last page that lie beyond the sequence are zeroed in
+//     shared memory before the product, so that leftovers of an earlier tenant of the page cannot reach the sum
+//     (0 * inf).
+// Two blocks fit on an SM (98 KB of shared memory and 256 columns of tensor memory each); while one waits for its
 // softmax the other's products keep the tensor core busy. A block's own chain per page (scores -> softmax -> P ->
 // product) is what bounds a single long prompt; many sequences or heads fill the GPU.
 //
@@ -46,6 +50,7 @@ struct AttnTcArgs {
   const int* block_table;       // [n, table_stride]
   int table_stride;
   int heads, kv_heads, window;
+  int sms;                      // multiprocessors of the device (block order)
   float scale_log2;
   int* status;
 };
@@ -65,17 +70,16 @@ template <int HD>
 struct AttnTcLayout {
   static constexpr int Q_BYTES = kAtRows * HD * 2;
   static constexpr int KV_BYTES = 64 * HD * 2;       // one page tile
-  static constexpr int P_BYTES = kAtRows * 64 * 2;
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + Q_BYTES;      // two stages
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES; // two stages
-  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int SUM_OFF = V_OFF + 2 * KV_BYTES;        // the halves' row sums, float [2 halves][128 rows]
+  static constexpr int BAR_OFF = SUM_OFF + 2 * kAtRows * 4;
   static constexpr int N_BARS = 12;
-  static constexpr int XCH_OFF = BAR_OFF + N_BARS * 8 + 16;   // row maxima as 16-bit values, [2 halves][128 rows]
-  static constexpr int TOTAL = XCH_OFF + 2 * kAtRows * 2;
+  static constexpr int XCH_OFF = BAR_OFF + N_BARS * 8 + 16;   // row maxima as 16-bit values, [2 pages][2 halves][128 rows]
+  static constexpr int TOTAL = XCH_OFF + 4 * kAtRows * 2;
   static_assert(2 * (TOTAL + 1024) <= 228 * 1024, "two blocks must fit on an SM");
-  static constexpr int TMEM_COLS = 256;              // S0, S1 (64 each) and O (HD <= 128)
+  static constexpr int TMEM_COLS = 256;              // S0, S1 (64 each; P_j takes the first 32 of S_j's) and O (HD <= 128)
 };
 
 template <int HD>
@@ -90,18 +94,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (threadIdx.x == 0) atomicExch(a.status, 20);
     return;
   }
-  const uint32_t sQ = base + L::Q_OFF, sK = base + L::K_OFF, sV = base + L::V_OFF, sP = base + L::P_OFF;
+  const uint32_t sQ = base + L::Q_OFF, sK = base + L::K_OFF, sV = base + L::V_OFF;
   const uint32_t bars = base + L::BAR_OFF;
-  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, s_full = bars + 40, s_empty = bars + 56,
-                 pv_done = bars + 72, p_full = bars + 88;
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, s_full = bars + 40, p_full = bars + 56,
+                 pv_done = bars + 72;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + L::N_BARS * 8);
 
-  const int seq = blockIdx.z, kh = blockIdx.y;
+  // Which tile a block takes. Blocks start in the order of their index, two to an SM, and a late tile of a prompt
+  // walks many more pages than an early one. The first `sms` blocks take the longest tiles, longest first; if all
+  // blocks are on the GPU at once the rest come shortest first, so that (where the hardware hands out second places
+  // in the order of the first) the longest tiles share their SM with the shortest.
+  const int pairs = (int)(gridDim.y * gridDim.z), total = (int)gridDim.x * pairs;
+  const int lin = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  const int rank = (lin < a.sms || total > 2 * a.sms) ? lin : total - 1 - (lin - a.sms);
+  const int seq = (rank % pairs) / (int)gridDim.y, kh = (rank % pairs) % (int)gridDim.y;
   const int G = a.heads / a.kv_heads;
   const int count = a.counts[seq], past = a.past[seq], tok0 = a.seq_start[seq];
   const int rows_total = count * G;
   const int n_tiles = (rows_total + kAtRows - 1) / kAtRows;
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;    // heavy (late) tiles first
+  const int tile = (int)gridDim.x - 1 - rank / pairs;
   if (tile >= n_tiles) return;
   const int r0 = tile * kAtRows;
   const int t_first = r0 / G;
@@ -119,9 +130,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(v_full + 8 * i, 1);
       mbar_init(s_full + 8 * i, 1);
       mbar_init(pv_done + 8 * i, 1);
-      mbar_init(s_empty + 8 * i, 8);     // one arrival per softmax warp
+      mbar_init(p_full + 8 * i, 8);      // one arrival per softmax warp
     }
-    mbar_init(p_full, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -159,7 +169,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int j = 0; j < n_pages && ok; ++j) {
         const int s = j & 1;
         if (!mbar_wait(k_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 24); break; }
-        if (j >= 2 && !mbar_wait(s_empty + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 25); break; }   // the softmax has read S_{j-2}
+        // S_j lands where S_{j-2} and then P_{j-2} lay: the product that read P_{j-2} must be through
+        if (j >= 2 && !mbar_wait(pv_done + 8 * s, ((j >> 1) - 1) & 1)) { atomicExch(a.status, 25); break; }
         tc_fence_after();
 #pragma unroll
         for (int h = 0; h < HD / 64; ++h) {
@@ -191,15 +202,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int j = 0; j < n_pages; ++j) {
         const int s = j & 1;
         if (!mbar_wait(v_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 27); break; }
-        if (!mbar_wait(p_full, j & 1)) { atomicExch(a.status, 26); break; }
+        // a barrier per score buffer: the softmax may be a page ahead of this warp, never two
+        if (!mbar_wait(p_full + 8 * s, (j >> 1) & 1)) { atomicExch(a.status, 26); break; }
         tc_fence_after();
-        const uint64_t dp = smem_desc(sP);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {      // 16 keys each: 32 bytes along a row of P, two 8-key groups of V
+        for (int k4 = 0; k4 < 4; ++k4) {      // 16 keys each: 8 columns of P in tensor memory, two 8-key groups of V
           const uint64_t dv = smem_desc_mn(sV + s * L::KV_BYTES + k4 * 2048, 8192, 1024);
-          mma_bf16_ss(tO, dp + (uint64_t)(k4 * 2), dv, idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
+          mma_bf16_ts(tO, tmem + (uint32_t)(s * 64 + k4 * 8), dv, idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
         }
-        mma_commit(pv_done + 8 * s);         // P and this value stage are free again when it fires
+        mma_commit(pv_done + 8 * s);         // this score buffer and this value stage are free again when it fires
         if (j + 1 < n_pages) {
           if (j >= 1 && !mbar_wait(pv_done + 8 * (s ^ 1), ((j - 1) >> 1) & 1)) { atomicExch(a.status, 22); break; }
           load_values(j + 1);
@@ -215,7 +226,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int pos = R < rows_total ? past + R / G : -1;        // -1: a padding row sees nothing
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 halves][128 rows]
+    unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 pages][2 halves][128 rows]
     float m_used = -INFINITY, l = 0.0f;
     // A wait that gives up ends nothing here: the warp notes it, stops waiting and walks on to the end, because its
     // partner (the warp with the other half of the same rows) meets it at a hardware barrier twice per page and
@@ -236,13 +247,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int j = 0; j < n_pages; ++j) {
       const int b = j & 1, key0 = (page_lo + j) * 64 + half * 32;
       if (!s_ready) wait_warp(s_full + 8 * b, (j >> 1) & 1, 28);
-      // asked now, needed after the maximum: has the last product finished (P free, O complete)?
-      const uint32_t pv_ready = j > 0 ? mbar_test(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1) : 1u;
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(lane_addr + (uint32_t)(b * 64 + half * 32), sr);
-      tc_fence_before();
-      arrive_warp(s_empty + 8 * b);
 
       // raw scores -> masked raw scores and their maximum; the mask costs two compares and a select per score, so
       // only warps with a row that needs it (the diagonal, a window's edge, padding) run it
@@ -261,16 +268,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       {
         const uint32_t bits = __float_as_uint(mx);
         const unsigned short up = (unsigned short)(((bits & 0x80000000u) ? bits : bits + 0xffffu) >> 16);
-        if (j > 0) pair_sync();            // the partner has read the maximum of the last page
-        xch[half * 128 + r] = up;
+        // a place per page parity: when this is written again two pages on, the partner has passed the barrier of
+        // the page between, which it reaches only after reading this one
+        xch[b * 256 + half * 128 + r] = up;
         pair_sync();
-        const unsigned short other = xch[(half ^ 1) * 128 + r];
+        const unsigned short other = xch[b * 256 + (half ^ 1) * 128 + r];
         mx = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
       }
-      if (!pv_ready) wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29);
       const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29);      // O must hold all of the last product
         tc_fence_after();
         const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
 #pragma unroll
@@ -282,7 +290,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tmem_st16(lane_addr + 128 + half * (HD / 2) + c0, o);
         }
         l *= alpha;
-        tc_fence_before();
       }
       if (grow) m_used = m_new;
       const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
@@ -300,12 +307,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       l += l0 + l1;
       // asked now, needed at the top of the next page: are its scores complete?
       s_ready = j + 1 < n_pages ? mbar_test(s_full + 8 * (b ^ 1), ((j + 1) >> 1) & 1) : 0u;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const uint32_t dst = sP + (uint32_t)(r * 128 + (((half * 4 + ch) ^ (r & 7)) << 4));
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * ch]), "r"(pk[4 * ch + 1]),
-                     "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3]) : "memory");
-      }
+      // P_j goes where S_j was: both threads of the row have read their scores (they met at the barrier above), and
+      // the product that read P_{j-2} from these columns finished before S_j was written
+      tmem_st16(lane_addr + (uint32_t)(b * 64 + half * 16), pk);
       const int valid = seq_len - (page_lo + j) * 64;          // rows of this page that belong to the sequence
       if (valid < 64) {
         wait_warp(v_full + 8 * b, (j >> 1) & 1, 31);
@@ -316,38 +320,53 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
           }
         }
+        fence_smem_to_async();
       }
-      fence_smem_to_async();
-      arrive_warp(p_full);
+      tc_fence_before();
+      arrive_warp(p_full + 8 * b);
     }
     wait_warp(pv_done + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, 32);
     {
       tc_fence_after();
-      // the row's sum is the two halves' sums; they meet in the P tile, which the last product has finished reading
-      float* xl = reinterpret_cast<float*>(smem + L::P_OFF);
+      // the row's sum is the two halves' sums
+      float* xl = reinterpret_cast<float*>(smem + L::SUM_OFF);
       xl[half * 128 + r] = l;
       pair_sync();
-      if (ok) {
-        l += xl[(half ^ 1) * 128 + r];
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        __nv_bfloat16* dst = a.out + ((size_t)(tok0 + (R < rows_total ? R / G : 0)) * a.heads + kh * G + R % G) * HD + half * (HD / 2);
+      l += xl[(half ^ 1) * 128 + r];
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      // this thread's half of the accumulator row: all loads under way at once, one wait
+      uint32_t o[HD / 2];
 #pragma unroll
-        for (int c0 = 0; c0 < HD / 2; c0 += 16) {
-          uint32_t o[16];
-          tmem_ld16(lane_addr + 128 + half * (HD / 2) + c0, o);
-          if (R < rows_total) {
+      for (int c0 = 0; c0 < HD / 2; c0 += 16) tmem_ld16_nowait(lane_addr + 128 + half * (HD / 2) + c0, o + c0);
+      tmem_wait_ld();
+      // A lane holds a row, so a warp's store would touch 32 lines at once. The normalised rows go through shared
+      // memory instead, into the query tile's place (the last score product has read it): rows of HD * 2 bytes, the
+      // 16-byte pieces of each 128 bytes exchanged by the row's low bits so that a warp's 32 rows spread over the banks.
 #pragma unroll
-            for (int c = 0; c < 16; c += 8) {
-              uint4 q;
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-              q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
-              q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
-              *reinterpret_cast<uint4*>(dst + c0 + c) = q;
-            }
-          }
+      for (int c = 0; c < HD / 2; c += 8) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+        const int piece = (half * (HD / 2) + c) >> 3;
+        const uint32_t dst = sQ + (uint32_t)(r * (HD * 2) + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h0)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
+      }
+      asm volatile("bar.sync 5, 256;" ::: "memory");      // the eight softmax warps
+      // each warp stores sixteen rows, its lanes along a row: whole 128-byte lines
+      constexpr int kPieces = HD / 8, kRowsAtOnce = 32 / kPieces;
+      const int piece = lane % kPieces;
+#pragma unroll
+      for (int it = 0; it < 16 / kRowsAtOnce; ++it) {
+        const int rr = (warp - 2) * 16 + it * kRowsAtOnce + lane / kPieces;
+        const int Rr = r0 + rr;
+        if (ok && Rr < rows_total) {
+          const uint32_t src = sQ + (uint32_t)(rr * (HD * 2) + (((piece & ~7) | ((piece ^ rr) & 7)) << 4));
+          uint4 q;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(src) : "memory");
+          *reinterpret_cast<uint4*>(a.out + ((size_t)(tok0 + Rr / G) * a.heads + kh * G + Rr % G) * HD + piece * 8) = q;
         }
       }
     }
@@ -438,7 +457,7 @@ extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v
   AttnTcArgs a;
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.window = window;
-  a.scale_log2 = scale * 1.4426950408889634f; a.status = status;
+  a.scale_log2 = scale * 1.4426950408889634f; a.status = status; a.sms = sm_count();
   return head_dim == 64 ? launch_attn_tc<64>(mq, mk, mv, a, n_seqs, max_count, (cudaStream_t)stream)
                         : launch_attn_tc<128>(mq, mk, mv, a, n_seqs, max_count, (cudaStream_t)stream);
 }
