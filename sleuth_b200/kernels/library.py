@@ -138,7 +138,7 @@ _SIGNATURES = {
     "slb_qkv_post": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "slb_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "slb_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
-    "slb_attention_tc": [P, P, P, P, P, P, P, P, I, I, I, L, L, I, I, I, I, F, P, P],
+    "slb_attention_tc": [P, P, P, P, P, P, P, P, I, I, I, L, L, I, I, I, I, F, P, I, I, P],
     "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, I, P, P, P, P, P, F, P, L, P],
     "slb_gemm_skinny": [P, P, P, I, I, I, I, I, P, L, P, I, P],
     "slb_gemm_skinny_norm": [P, P, F, P, P, I, I, I, I, I, P, L, P, I, P],

@@ -197,9 +197,12 @@ def attention_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torc
 
 
 def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
-                 kv_heads: int, head_dim: int, window: int, scale: float, stream=None) -> None:
+                 kv_heads: int, head_dim: int, window: int, scale: float, stream=None, wide: bool | None = None,
+                 max_keys: int = 0) -> None:
     """Attention for a step in which sequences bring many tokens, on the tcgen05 tensor cores (same contract as
-    ``attention_prefill``). A bounded wait that gave up inside the kernel shows in ``tc_check``."""
+    ``attention_prefill``). A bounded wait that gave up inside the kernel shows in ``tc_check``. ``wide``: the
+    kernel that walks two pages a step (True), one page a step (False), or the library's choice from the step's
+    shape; ``max_keys`` (the most keys a sequence has after this step, 0 = not known) helps that choice."""
     _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
@@ -210,7 +213,8 @@ def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, m
     _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
     lib().call("slb_attention_tc", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), T, k_pool.shape[0], heads, kv_heads, head_dim,
-               int(window), float(scale), _p(_tc_status(q.device)), stream if stream is not None else current_stream())
+               int(window), float(scale), _p(_tc_status(q.device)), -1 if wide is None else int(bool(wide)),
+               int(max_keys), stream if stream is not None else current_stream())
 
 
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,

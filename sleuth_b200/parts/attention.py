@@ -103,7 +103,7 @@ class GQAAttention(Part):
                                  s.head_dim, view.window, self.scale, splits, scratch, b.stream)
         elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
             ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
+                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, max_keys=b.max_len)
         else:
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
                                   s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)

@@ -177,9 +177,10 @@ def run_attention(kind, dtype, heads, kv_heads, hd, pasts, counts, window, seed,
     elif kind == "prefill":
         o.attention_prefill(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)),
                             d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale)
-    elif kind == "tc":
+    elif kind in ("tc", "tc one page a step", "tc two pages a step"):
         o.attention_tc(d(q), d(k_pool), d(v_pool), out, d(starts), d(np.asarray(pasts, dtype=np.int32)),
-                       d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale)
+                       d(np.asarray(counts, dtype=np.int32)), d(table), max(counts), heads, kv_heads, hd, window, scale,
+                       wide=None if kind == "tc" else kind == "tc two pages a step")
         o.gemm_tc_check(DEV)
     else:
         splits = kind
@@ -208,16 +209,27 @@ def test_attention_prefill_tensor_cores(heads, kv_heads, hd):
     run_attention("prefill", bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
 
 
+@pytest.mark.parametrize("kind", ["tc one page a step", "tc two pages a step"])
 @pytest.mark.parametrize("heads,kv_heads,hd", [(4, 2, 128), (4, 1, 64), (8, 8, 64), (16, 2, 128), (2, 2, 128), (32, 1, 64)])
-def test_attention_tcgen05(heads, kv_heads, hd):
-    """The tcgen05 kernel on the cases of the mma.sync kernel (pools are NaN outside the sequences), and on
-    longer prompts that cross many pages and tiles."""
+def test_attention_tcgen05(heads, kv_heads, hd, kind):
+    """Both tcgen05 kernels on the cases of the mma.sync kernel (pools are NaN outside the sequences), and on
+    longer prompts that cross many pages and tiles, with even and odd numbers of pages, windows that end inside a
+    step's first or second page, and sequences that end in either."""
     bf = torch.bfloat16
-    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 0, 0], counts=[1, 64, 200], window=0, seed=1)
-    run_attention("tc", bf, heads, kv_heads, hd, pasts=[70, 0, 129, 5], counts=[33, 5, 1, 130], window=0, seed=2)
-    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 150], counts=[170, 40], window=50, seed=3)
-    run_attention("tc", bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
-    run_attention("tc", bf, heads, kv_heads, hd, pasts=[0, 37], counts=[700, 450], window=0, seed=5)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[0, 0, 0], counts=[1, 64, 200], window=0, seed=1)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[70, 0, 129, 5], counts=[33, 5, 1, 130], window=0, seed=2)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[0, 150], counts=[170, 40], window=50, seed=3)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[300], counts=[7], window=64, seed=4)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[0, 37], counts=[700, 450], window=0, seed=5)
+    run_attention(kind, bf, heads, kv_heads, hd, pasts=[64, 0, 500], counts=[321, 128, 90], window=200, seed=6)
+
+
+def test_attention_tcgen05_chooses_by_shape():
+    """Left to itself the library takes the two-page kernel where one round of blocks holds the step or the longest
+    tile outweighs an SM's share of all pages, the one-page kernel where many short tiles fill the GPU."""
+    bf = torch.bfloat16
+    run_attention("tc", bf, 4, 2, 128, pasts=[0, 10], counts=[511, 60], window=0, seed=7)          # few blocks
+    run_attention("tc", bf, 16, 8, 128, pasts=[0] * 12, counts=[200] * 12, window=0, seed=8)       # many short tiles
 
 
 def test_attention_tcgen05_growing_scores():
@@ -239,13 +251,14 @@ def test_attention_tcgen05_growing_scores():
         q[:, :, 0] = 8.0
         d = lambda a: torch.as_tensor(a).to(DEV)
         i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
-        out = torch.empty(L, H * hd, dtype=bf, device=DEV)
-        o.attention_tc(d(q), d(k_pool), d(v_pool), out, i32(0, L), i32(0), i32(L), d(table), L, H, K, hd, 0, 1.0)
-        o.gemm_tc_check(DEV)
         ref = plain_attention(q.double(), ks[0].double(), vs[0].double(), list(range(L)), 0, 1.0)
-        got = out.cpu().double().view(L, H, hd)
-        assert torch.isfinite(got).all()
-        torch.testing.assert_close(got, ref, rtol=2e-2, atol=1.5e-2)
+        for wide in (False, True):
+            out = torch.empty(L, H * hd, dtype=bf, device=DEV)
+            o.attention_tc(d(q), d(k_pool), d(v_pool), out, i32(0, L), i32(0), i32(L), d(table), L, H, K, hd, 0, 1.0, wide=wide)
+            o.gemm_tc_check(DEV)
+            got = out.cpu().double().view(L, H, hd)
+            assert torch.isfinite(got).all()
+            torch.testing.assert_close(got, ref, rtol=2e-2, atol=1.5e-2)
 
 
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
