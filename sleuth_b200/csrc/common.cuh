@@ -172,6 +172,29 @@ inline cudaError_t launch_with(bool early, void (*kernel)(KArgs...), dim3 grid, 
   return e;
 }
 
+// The same for kernels whose blocks come in clusters of `cluster` along x (the grid's x must be a multiple of it).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_clusters(bool early, unsigned cluster, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                   size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = early ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) note_launch_error(e);
+  return e;
+}
+
 // Ordinary kernels: allowed to start early only in mode 1. Kernels that fetch weights before their wait: modes 1 and 2.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -27,7 +27,7 @@ constexpr int kTcBM = 128;
 constexpr int kTcBK = 64;             // bf16 elements per slice: 128 bytes, one swizzle row
 // TMA stages: as many as fit in 192 KB (at most 8). What is in flight per SM bounds the operand stream (latency x
 // bandwidth), so narrow tiles, whose stages are small, get more of them.
-constexpr int tc_stages(int bn) {
+__host__ __device__ constexpr int tc_stages(int bn) {
   const int n = (192 * 1024) / ((kTcBM + bn) * kTcBK * 2);
   return n > 8 ? 8 : n;
 }
@@ -61,6 +61,21 @@ struct TcQkv {
   int table_stride, heads, kv_heads, head_dim;
   float eps;
 };
+
+// 32-byte accesses of one thread (addresses aligned to 32 bytes).
+__device__ __forceinline__ void ld_global_256(const float* p, float (&v)[8]) {
+  asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p));
+}
+// (memory that this kernel also writes: not through the read-only path)
+__device__ __forceinline__ void ld_global_256_rw(const float* p, float (&v)[8]) {
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
 
 // One head of one row: `taddr` is this thread's lane at the head's first accumulator column. Two passes over the
 // accumulator keep the registers few: the first sums the squares, the second takes the channels in the pairs that
@@ -132,15 +147,18 @@ __device__ __forceinline__ void qkv_head_epilogue(const TcQkv& q, uint32_t taddr
         y[j] = (y[j] * inv) * u.x; y[j + 1] = (y[j + 1] * inv) * u.y; y[j + 2] = (y[j + 2] * inv) * u.z; y[j + 3] = (y[j + 3] * inv) * u.w;
       }
     }
+    // A lane holds a row, so each of its loads and stores touches a line of its own: 32 bytes at a time (the widest
+    // there is) halves what the load/store unit has to do for the rotation factors and for the results.
     if (rotate) {
       const float* cs = q.cos_table + (size_t)pos * HALF + c0;
       const float* sn = q.sin_table + (size_t)pos * HALF + c0;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 co = *reinterpret_cast<const float4*>(cs + j), si = *reinterpret_cast<const float4*>(sn + j);
-        const float cc[4] = {co.x, co.y, co.z, co.w}, sv[4] = {si.x, si.y, si.z, si.w};
+      for (int j = 0; j < 32; j += 8) {
+        float cc[8], sv[8];
+        ld_global_256(cs + j, cc);
+        ld_global_256(sn + j, sv);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 8; ++e) {
           const float a0 = x[j + e], b0 = y[j + e];
           x[j + e] = a0 * cc[e] + (-b0) * sv[e];
           y[j + e] = b0 * cc[e] + a0 * sv[e];
@@ -148,18 +166,20 @@ __device__ __forceinline__ void qkv_head_epilogue(const TcQkv& q, uint32_t taddr
       }
     }
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      uint4 o;
-      __nv_bfloat162 p0 = __floats2bfloat162_rn(x[j], x[j + 1]), p1 = __floats2bfloat162_rn(x[j + 2], x[j + 3]);
-      __nv_bfloat162 p2 = __floats2bfloat162_rn(x[j + 4], x[j + 5]), p3 = __floats2bfloat162_rn(x[j + 6], x[j + 7]);
-      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-      *reinterpret_cast<uint4*>(dst + c0 + j) = o;
-      p0 = __floats2bfloat162_rn(y[j], y[j + 1]); p1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
-      p2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]); p3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
-      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-      *reinterpret_cast<uint4*>(dst + HALF + c0 + j) = o;
+    for (int j = 0; j < 32; j += 16) {
+      uint32_t o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        __nv_bfloat162 p = __floats2bfloat162_rn(x[j + 2 * e], x[j + 2 * e + 1]);
+        o[e] = *reinterpret_cast<uint32_t*>(&p);
+      }
+      st_global_256(dst + c0 + j, o);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        __nv_bfloat162 p = __floats2bfloat162_rn(y[j + 2 * e], y[j + 2 * e + 1]);
+        o[e] = *reinterpret_cast<uint32_t*>(&p);
+      }
+      st_global_256(dst + HALF + c0 + j, o);
     }
   }
 }
@@ -171,7 +191,18 @@ __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, 
   const bool full = col0 + 32 <= a.N;
   if (a.mode == kTcBf16 || a.mode == kTcSwiglu) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.ldc + col0;
-    if (full && (a.ldc % 8 == 0)) {
+    if (full && (a.ldc % 16 == 0) && ((uintptr_t)a.C % 32 == 0)) {      // 32 bytes at a time (a lane holds a row)
+#pragma unroll
+      for (int j = 0; j < 32; j += 16) {
+        uint32_t o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          __nv_bfloat162 p = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+          o[e] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        st_global_256(dst + j, o);
+      }
+    } else if (full && (a.ldc % 8 == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         uint4 q;
@@ -188,7 +219,22 @@ __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, 
     }
   } else {
     float* dst = reinterpret_cast<float*>(a.C) + (size_t)row * a.ldc + col0;
-    if (full && (a.ldc % 4 == 0)) {
+    if (full && (a.ldc % 8 == 0) && ((uintptr_t)a.C % 32 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint32_t o[8];
+        if (a.mode == kTcAddF32) {
+          float old[8];
+          ld_global_256_rw(dst + j, old);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(old[e] + v[j + e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(v[j + e]);
+        }
+        st_global_256(dst + j, o);
+      }
+    } else if (full && (a.ldc % 4 == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -210,14 +256,26 @@ __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, 
 // memory alternate, so the epilogue warps drain tile t while the tensor core already works on tile t + 1.
 // The q/k/v form has eight epilogue warps, two per quarter of the rows, each taking half of the tile's heads: its
 // epilogue is long, and what of it the next tile's products do not hide shows at the end of the kernel.
-template <int BN, bool QKV>
+//
+// PAIR: two blocks of a cluster share a tile of 256 rows (cta_group::2). Each loads its own 128 rows of X and half of
+// the tile's rows of W (for the gated form: one the gate rows, the other the up rows), the even block issues one
+// instruction for both, and each finds its 128 rows of the result in its own tensor memory. A block's shared
+// memory then serves half as many bytes per product (what bounds the single block: 12 KB read per 128-cycle
+// instruction beside TMA's writes), and a stage holds half as much, so twice as many are in flight. A stage's "full"
+// barrier is the even block's and counts both blocks' loads; commits arrive at both blocks' barriers; the odd
+// block's epilogue warps hand the accumulator back at the even block's barrier.
+template <int BN, bool QKV, bool PAIR>
 __global__ void __launch_bounds__(QKV ? kTcThreads + 128 : kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a, TcQkv qa) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BN * kTcBK * 2, STAGE = A_BYTES + B_BYTES;
-  constexpr int S = tc_stages(BN);
+  constexpr int BROWS = PAIR ? BN / 2 : BN;          // rows of W in this block's shared memory
+  constexpr int A_BYTES = kTcBM * kTcBK * 2, B_BYTES = BROWS * kTcBK * 2, STAGE = A_BYTES + B_BYTES;
+  constexpr int S = tc_stages(BROWS);
+  constexpr int kRows = PAIR ? 2 * kTcBM : kTcBM;    // rows of a tile
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int n_workers = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x, worker = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * STAGE);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * S, tfull0 = empty0 + 8 * S, tempty0 = tfull0 + 16;
@@ -226,7 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool gated = a.mode == kTcSwiglu;
   const int cols_per_tile = gated ? BN / 2 : BN;
-  const int m_tiles = (a.M + kTcBM - 1) / kTcBM, n_tiles = (a.N + cols_per_tile - 1) / cols_per_tile;
+  const int m_tiles = (a.M + kRows - 1) / kRows, n_tiles = (a.N + cols_per_tile - 1) / cols_per_tile;
   const int total = m_tiles * n_tiles;
   const int k_tiles = (a.K + kTcBK - 1) / kTcBK;
 
@@ -237,17 +295,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull0 + 8 * i, 1);
-      mbar_init(tempty0 + 8 * i, QKV ? 8 : 4);        // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * i, (QKV ? 8 : 4) * (PAIR ? 2 : 1));        // one arrival per epilogue warp (of both blocks)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {     // one warp allocates both accumulators: 2 * BN columns of tensor memory
     __syncwarp();
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(2 * BN) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {      // the same warp of each block of the pair
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(2 * BN) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(2 * BN) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();      // both blocks' barriers and tensor memory are there
+  else __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
@@ -259,8 +323,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // ---- producer ----
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+      for (int tile = worker; tile < total && ok; tile += n_workers) {
+        const int m0 = (tile % m_tiles) * kRows + (int)rank * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % S;
           if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1)) {
@@ -269,23 +333,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             break;
           }
           const uint32_t sa = tiles + s * STAGE, sb = sa + A_BYTES;
-          mbar_expect_tx(full0 + 8 * s, STAGE);
-          tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
-          tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
-          if (gated) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
-          else if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+          if constexpr (PAIR) {
+            // the even block's barrier counts the bytes of both; this block's half of W's rows: the gate rows or the
+            // up rows of the gated form, the first or the second half of the tile's columns otherwise
+            const uint32_t full = cluster_map(full0 + 8 * s, 0);
+            if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);
+            const int w_row = gated ? (rank ? a.up_row0 + n0 : n0) : n0 + (int)rank * BROWS;
+            tma_load_2d_pair(sa, &map_x, kt * kTcBK, m0, full);
+            tma_load_2d_pair(sb, &map_w, kt * kTcBK, w_row, full);
+          } else {
+            mbar_expect_tx(full0 + 8 * s, STAGE);
+            tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
+            tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
+            if (gated) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
+            else if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+          }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 && rank == 0) {
     // ---- MMA issuer: the whole warp walks the loop (its counters and descriptors then live in uniform registers),
-    // one lane issues the products and the commits ----
-    constexpr uint32_t idesc = instr_desc(kTcBM, BN);
+    // one lane issues the products and the commits; of a pair, the even block's ----
+    constexpr uint32_t idesc = instr_desc(kRows, BN);
     constexpr uint32_t kAll = 0xffffffffu;
     int it = 0, t = 0;
     bool ok = true;
     bool next_ready = false;
-    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++t) {
+    for (int tile = worker; tile < total && ok; tile += n_workers, ++t) {
       const int buf = t & 1;
       if (t >= 2 && !__all_sync(kAll, mbar_wait(tempty0 + 8 * buf, ((t / 2) - 1) & 1))) {   // the epilogue has drained this accumulator
         if (lane == 0) atomicExch(a.status, 4);
@@ -309,22 +383,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const uint64_t da = smem_desc(sa), db = smem_desc(sb);
         if (lane == 0) {
 #pragma unroll
-          for (int k4 = 0; k4 < kTcBK / 16; ++k4)    // 16 elements = 32 bytes further along K inside the swizzle row
-            mma_bf16_ss(acc, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
-          mma_commit(empty0 + 8 * s);                // fires when these MMAs have read the stage
+          for (int k4 = 0; k4 < kTcBK / 16; ++k4) {  // 16 elements = 32 bytes further along K inside the swizzle row
+            if constexpr (PAIR) mma_bf16_ss_pair(acc, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+            else mma_bf16_ss(acc, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
+          }
+          if constexpr (PAIR) mma_commit_pair(empty0 + 8 * s);      // both blocks' stages
+          else mma_commit(empty0 + 8 * s);           // fires when these MMAs have read the stage
         }
         next_ready = __all_sync(kAll, probe != 0);
       }
-      if (ok && lane == 0) mma_commit(tfull0 + 8 * buf);        // fires when the whole tile has been accumulated
+      if (ok && lane == 0) {                                    // fires when the whole tile has been accumulated
+        if constexpr (PAIR) mma_commit_pair(tfull0 + 8 * buf);
+        else mma_commit(tfull0 + 8 * buf);
+      }
       __syncwarp();
     }
-  } else {
+  } else if (warp >= 2) {
     // ---- epilogue: warps 2..5, tensor-memory lanes 32 * (warp % 4) .. + 31 ----
     const int quad = warp & 3;
+    const uint32_t tempty_at = PAIR ? cluster_map(tempty0, 0) : tempty0;      // the issuing block's barriers
     int t = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++t) {
+    for (int tile = worker; tile < total; tile += n_workers, ++t) {
       const int buf = t & 1;
-      const int m0 = (tile % m_tiles) * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+      const int m0 = (tile % m_tiles) * kRows + (int)rank * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
       const int row = m0 + quad * 32 + lane;
       // Adding into the stream: the old values of this thread's row are fetched while the products still run, so
       // that the epilogue (which nothing hides when a block has a single tile) does not wait for them.
@@ -333,15 +414,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // (the whole warp or none of it: the tensor-memory loads are collective; a warp with rows beyond the matrix
       // takes the general path)
       const bool preloaded = kPreload && __all_sync(0xffffffffu, a.mode == kTcAddF32 && row < a.M && n0 + BN <= a.N &&
-                                                                    (a.ldc % 4 == 0));
+                                                                    (a.ldc % 8 == 0) && ((uintptr_t)a.C % 32 == 0));
       if constexpr (kPreload) {
         if (preloaded) {
-          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.C) + (size_t)row * a.ldc + n0);
+          const float* src = reinterpret_cast<const float*>(a.C) + (size_t)row * a.ldc + n0;
 #pragma unroll
-          for (int j = 0; j < BN / 4; ++j) {
-            const float4 o = src[j];
-            old[4 * j] = o.x; old[4 * j + 1] = o.y; old[4 * j + 2] = o.z; old[4 * j + 3] = o.w;
-          }
+          for (int j = 0; j < BN; j += 8) ld_global_256_rw(src + j, *reinterpret_cast<float(*)[8]>(&old[j]));
         }
       }
       bool ready = true;
@@ -361,14 +439,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             uint32_t r[32];
             tmem_ld32(lane_base + c, r);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(dst + c + j) =
-                  make_float4(old[c + j] + __uint_as_float(r[j]), old[c + j + 1] + __uint_as_float(r[j + 1]),
-                              old[c + j + 2] + __uint_as_float(r[j + 2]), old[c + j + 3] + __uint_as_float(r[j + 3]));
+            for (int j = 0; j < 32; j += 8) {
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(old[c + j + e] + __uint_as_float(r[j + e]));
+              st_global_256(dst + c + j, o);
+            }
           }
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(tempty_at + 8 * buf);
+            else mbar_arrive(tempty0 + 8 * buf);
+          }
           continue;
         }
       }
@@ -398,13 +481,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // this warp has read its part of the accumulator: let the tensor core have the buffer back
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(tempty_at + 8 * buf);
+        else mbar_arrive(tempty0 + 8 * buf);
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 2)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  if constexpr (PAIR) {
+    cluster_sync_all();        // neither block frees tensor memory, or leaves, while the other may still be signalled
+    if (warp == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  } else {
+    __syncthreads();
+    if (warp == 2)
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  }
 }
 
 // What every tensor-memory kernel here does when one of its waits runs out, as a kernel of its own, so that the
@@ -450,22 +542,45 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-template <int BN, bool QKV = false>
+template <int BN, bool QKV = false, bool PAIR = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t s, const TcQkv& qa = TcQkv{}) {
-  constexpr int kStages = tc_stages(BN);
-  const int smem = kStages * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * kStages + 4) * 8 + 16 + 1024;
+  constexpr int kBRows = PAIR ? BN / 2 : BN;
+  constexpr int kStages = tc_stages(kBRows);
+  const int smem = kStages * (kTcBM * kTcBK * 2 + kBRows * kTcBK * 2) + (2 * kStages + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, QKV, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(2, "gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   const int cols_per_tile = a.mode == kTcSwiglu ? BN / 2 : BN;
-  const long long total = (long long)((a.N + cols_per_tile - 1) / cols_per_tile) * ((a.M + kTcBM - 1) / kTcBM);
+  const int rows_per_tile = PAIR ? 2 * kTcBM : kTcBM;
+  const long long total = (long long)((a.N + cols_per_tile - 1) / cols_per_tile) * ((a.M + rows_per_tile - 1) / rows_per_tile);
   const int sms = sm_count();
-  dim3 grid((unsigned)(total < sms ? total : sms));
-  launch_prefetching(gemm_tc_kernel<BN, QKV>, grid, dim3(QKV ? kTcThreads + 128 : kTcThreads), (size_t)smem, s, mx, mw, a, qa);
+  const dim3 block(QKV ? kTcThreads + 128 : kTcThreads);
+  if (PAIR) {
+    const long long pairs = sms / 2;
+    dim3 grid((unsigned)(2 * (total < pairs ? total : pairs)));
+    launch_clusters(pdl_mode() != 0, 2, gemm_tc_kernel<BN, QKV, PAIR>, grid, block, (size_t)smem, s, mx, mw, a, qa);
+  } else {
+    dim3 grid((unsigned)(total < sms ? total : sms));
+    launch_prefetching(gemm_tc_kernel<BN, QKV, PAIR>, grid, block, (size_t)smem, s, mx, mw, a, qa);
+  }
   return check_launch("gemm_tc");
+}
+
+// Whether two blocks share tiles of 256 rows. SLEUTH_B200_GEMM_PAIR=0/1 decides for every product of at least 256
+// rows; otherwise pairs take the products of many rows, where they were measured faster (Qwen3-0.6B shapes, one
+// B200: level at 2,048 rows, 3 to 12 % faster from 4,096 on, slower below 2,048). The q/k/v form, whose epilogue
+// weighs more than its products, gained nothing below 16,384 rows and stays with single blocks.
+static bool pair_pays(int M) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = getenv("SLEUTH_B200_GEMM_PAIR");
+    forced = e ? (e[0] == '0' ? 0 : 1) : -1;
+  }
+  if (M < 256) return false;
+  return forced >= 0 ? forced != 0 : M >= 4096;
 }
 
 }  // namespace slb
@@ -497,21 +612,24 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
   // within one round a narrower tile is a little faster (more SMs stream operands), while a second round costs
   // nearly twice (768 rows: 17 us with 96 tiles of 64 columns, 28 us with 192 of 32). When even the widest tile
   // needs several rounds, the widest is the most efficient.
-  const long long m_tiles = (M + 127) / 128;
-  const int sms = sm_count();
+  const bool pair = pair_pays(M);
+  const long long m_tiles = pair ? (M + 255) / 256 : (M + 127) / 128;
+  const int sms = sm_count(), workers = pair ? sms / 2 : sms;
   int bn = 256;
-  for (int cand = gated ? 64 : 32; cand <= 256; cand <<= 1) {
+  for (int cand = pair ? 128 : (gated ? 64 : 32); cand <= 256; cand <<= 1) {
     const int cols = gated ? cand / 2 : cand;
-    if (m_tiles * ((N + cols - 1) / cols) <= sms) { bn = cand; break; }
+    if (m_tiles * ((N + cols - 1) / cols) <= workers) { bn = cand; break; }
   }
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, kTcBM);
   if (rc) return rc;
-  rc = make_map(&mw, W, gated ? 2ll * N : N, K, gated ? bn / 2 : (bn < 128 ? bn : 128));
+  // a block of a pair loads half of the tile's rows of W in one box; a single block loads boxes of at most 128 rows
+  rc = make_map(&mw, W, gated ? 2ll * N : N, K, gated || pair ? bn / 2 : (bn < 128 ? bn : 128));
   if (rc) return rc;
   TcArgs a;
   a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.mode = mode; a.up_row0 = N; a.status = status;
   cudaStream_t s = (cudaStream_t)stream;
+  if (pair) return bn == 256 ? launch_tc<256, false, true>(mx, mw, a, s) : launch_tc<128, false, true>(mx, mw, a, s);
   switch (bn) {
     case 256: return launch_tc<256>(mx, mw, a, s);
     case 128: return launch_tc<128>(mx, mw, a, s);
@@ -538,10 +656,11 @@ extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int h
   SLB_REQUIRE(q_out != nullptr && tok_pos != nullptr && status != nullptr, "gemm_tc_qkv: q_out, tok_pos and status are needed");
   SLB_REQUIRE(kv_heads == 0 || (k_pool && v_pool && tok_seq && block_table && table_stride > 0),
               "gemm_tc_qkv: the cache pools and the block table are needed to store keys and values");
-  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
-              ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
-              ((uintptr_t)q_gain % 16 == 0) && ((uintptr_t)k_gain % 16 == 0) && ((uintptr_t)cos_table % 16 == 0) &&
-              ((uintptr_t)sin_table % 16 == 0), "gemm_tc_qkv: every tensor must be 16-byte aligned");
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
+              ((uintptr_t)q_gain % 16 == 0) && ((uintptr_t)k_gain % 16 == 0), "gemm_tc_qkv: every tensor must be 16-byte aligned");
+  SLB_REQUIRE(((uintptr_t)q_out % 32 == 0) && ((uintptr_t)k_pool % 32 == 0) && ((uintptr_t)v_pool % 32 == 0) &&
+              ((uintptr_t)cos_table % 32 == 0) && ((uintptr_t)sin_table % 32 == 0),
+              "gemm_tc_qkv: q_out, the pools and the rotation tables must be 32-byte aligned (they are read and written 32 bytes at a time)");
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, kTcBM);
   if (rc) return rc;

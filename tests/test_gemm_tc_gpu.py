@@ -45,6 +45,14 @@ def test_gemm_tc(M, N, K, mode):
     run(M, N, K, mode)
 
 
+@pytest.mark.parametrize("M,N,K,mode", [(4100, 300, 136, "f32"), (4096, 512, 64, "bf16"), (4500, 1024, 200, "add"),
+                                         (4200, 136, 96, "swiglu"), (5000, 520, 72, "swiglu")])
+def test_gemm_tc_many_rows_take_pairs_of_blocks(M, N, K, mode):
+    """From 4,096 rows on two blocks of a cluster share tiles of 256 rows (cta_group::2): each loads its rows of X and
+    half of the tile's rows of W; row counts that end inside the upper or the lower half of the last tile."""
+    run(M, N, K, mode)
+
+
 @pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (256, 3072, 1024), (77, 136, 96), (2048, 200, 72)])
 def test_gemm_tc_gated_activation(M, inter, K):
     run(M, inter, K, "swiglu")
