@@ -87,6 +87,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                const __grid_constant__ CUtensorMap map_v, AttnTcArgs a) {
   using L = AttnTcLayout<HD>;
   extern __shared__ __align__(1024) unsigned char smem[];
+  Tracer trace(kTraceAttnTc);      // thread 0 issues the score products: past its wait, last scores issued, exit
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_addr(smem);
   if ((base & 1023u) != 0) {            // the swizzled tiles need 1024-byte alignment; refuse rather than compute nonsense
@@ -143,6 +144,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   pdl_launch_dependents();     // only now: a successor that also wants tensor memory must not take it before this block has its own
   pdl_wait();
+  trace.mark(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -186,6 +188,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         mma_commit(s_full + 8 * s);          // S_j is complete: the softmax may read it, and this key stage is free again
       }
+      trace.mark(2);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -415,6 +418,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, AttnTcArgs a) {
   using L = AttnWideLayout<HD>;
   extern __shared__ __align__(1024) unsigned char smem[];
+  Tracer trace(kTraceAttnTc);      // thread 0 issues the score products: past its wait, last scores issued, exit
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = smem_addr(smem);
   if ((base & 1023u) != 0) {
@@ -470,6 +474,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   pdl_launch_dependents();     // only now: a successor that also wants tensor memory must not take it before this block has its own
   pdl_wait();
+  trace.mark(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -520,6 +525,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         mma_commit(s_full + 8 * s);          // S_j is complete: the softmax may read it, and this key stage is free again
       }
+      trace.mark(2);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -763,6 +769,7 @@ static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(attention_tc)
 
 // 1 when the tcgen05 kernel takes this shape: bfloat16, head size 64 or 128, a group size that divides 128.
 extern "C" int slb_attention_tc_supported(int heads, int kv_heads, int head_dim) {

@@ -103,7 +103,7 @@ __device__ __forceinline__ void prefetch_page_item(const NextPages& p, int item,
 // six 64-bit words [kind | block << 16 | SM << 48, enter, mark 1, mark 2, mark 3, leave] to a buffer whose first word
 // counts the records. Each file with kernels keeps its own pointer to the buffer (slb_timeline_set_<file>).
 enum TraceKind : int { kTraceEmbed = 1, kTraceNorm, kTraceSkinny, kTraceDecodeAttention, kTraceArgmaxPart, kTraceArgmaxFinal,
-                       kTraceSample, kTraceOther };
+                       kTraceSample, kTraceOther, kTraceGemmTc, kTraceAttnTc };
 #ifdef SLB_TIMELINE
 static __device__ unsigned long long* g_timeline = nullptr;
 static __device__ unsigned int g_timeline_records = 0;

@@ -268,6 +268,7 @@ template <int BN, bool QKV, bool PAIR>
 __global__ void __launch_bounds__(QKV ? kTcThreads + 128 : kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a, TcQkv qa) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
+  Tracer trace(kTraceGemmTc);      // thread 0 is the producer: past its wait, all loads asked for, exit
   // tiles first (each a multiple of 1024 bytes, as the swizzle wants), barriers after
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int BROWS = PAIR ? BN / 2 : BN;          // rows of W in this block's shared memory
@@ -317,6 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   pdl_launch_dependents();
   pdl_wait();          // X is the previous kernel's output
+  trace.mark(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -350,6 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
         }
       }
+      trace.mark(2);
     }
   } else if (warp == 1 && rank == 0) {
     // ---- MMA issuer: the whole warp walks the loop (its counters and descriptors then live in uniform registers),
@@ -586,6 +589,7 @@ static bool pair_pays(int M) {
 }  // namespace slb
 
 using namespace slb;
+SLB_TIMELINE_SETTER(gemm_tc)
 
 // Runs the give-up path of the tensor-memory kernels on purpose, harmlessly (see tc_wait_probe_kernel): after it,
 // `status` holds `code`. polls: how often the one waiting thread looks at its barrier (1 to 1,000,000).

@@ -14,9 +14,9 @@ import torch
 
 from . import library
 
-FILES = ("gemm_skinny", "attention_flash", "elementwise", "sampling")
+FILES = ("gemm_skinny", "attention_flash", "elementwise", "sampling", "gemm_tc", "attention_tc")
 KINDS = {1: "embed", 2: "rmsnorm", 3: "gemm_skinny", 4: "attention_decode", 5: "argmax_partial", 6: "argmax_final",
-         7: "sample", 8: "other"}
+         7: "sample", 8: "other", 9: "gemm_tc", 10: "attention_tc"}
 _buffer = None
 
 
@@ -83,7 +83,8 @@ def launches(records: list[dict]) -> list[dict]:
 
 def main(argv=None) -> int:
     """``python -m sleuth_b200.kernels.timeline --config config.json --batch 8``: single-token steps of a model with
-    random weights, and where one of them spends its time, launch by launch (needs the -DSLB_TIMELINE build)."""
+    random weights, and where one of them spends its time, launch by launch (needs the -DSLB_TIMELINE build).
+    With ``--prompt-step`` the step looked at is the prompts' own (``--batch`` prompts of ``--prompt`` tokens)."""
     import argparse
     import json
 
@@ -96,12 +97,15 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=2048, help="tokens of each prompt")
     ap.add_argument("--layer", type=int, default=None, help="the layer to print launch by launch (default: the middle one)")
+    ap.add_argument("--prompt-step", action="store_true", help="look at the step that brings the prompts")
     args = ap.parse_args(argv)
     cfg = json.load(open(args.config))
     eng = Engine.from_config(cfg, seed=0, dtype="bf16", max_seq_len=args.prompt + 64, max_tokens=args.batch * (args.prompt + 64))
     rng = np.random.default_rng(0)
     V, B = cfg["vocab_size"], args.batch
     greedy = SamplingConfig(temperature=0.0)
+    if args.prompt_step:
+        return _prompt_step(eng, cfg, args, rng)
     slots = eng.open(B)
     eng.sampler.choose(eng.prefill(slots, [rng.integers(0, V, size=args.prompt).tolist() for _ in range(B)]), greedy)
     for _ in range(6):
@@ -136,6 +140,46 @@ def main(argv=None) -> int:
                   f"   {f(L['last_mark2'])}   {f(L['first_leave'])} {f(L['last_leave'])}   {(L['last_go'] - prev) / 1e3:6.2f} {(L['last_leave'] - prev) / 1e3:6.2f}")
             prev = L["last_leave"]
     eng.close(slots)
+    return 0
+
+
+
+def _prompt_step(eng, cfg, args, rng) -> int:
+    """The step that brings ``--batch`` prompts of ``--prompt`` tokens, four times (the shape repeats, so the later
+    ones are replayed graphs); the last one is printed launch by launch for one layer."""
+    V, B = cfg["vocab_size"], args.batch
+    prompts = [rng.integers(0, V, size=args.prompt).tolist() for _ in range(B)]
+    for _ in range(3):
+        slots = eng.open(B)
+        eng.prefill(slots, prompts)
+        eng.close(slots)
+    start(1 << 18)
+    slots = eng.open(B)
+    eng.prefill(slots, prompts)
+    step = launches(read())
+    eng.close(slots)
+    t0 = step[0]["first_enter"]
+    print(f"one prompt step: {len(step)} launches, {(step[-1]['last_leave'] - t0) / 1e3:.1f} us from the first entry to the last exit")
+    total, prev = {}, t0
+    for L in step:
+        n, us = total.get(L["kind"], (0, 0.0))
+        total[L["kind"]] = (n + 1, us + (L["last_leave"] - prev) / 1e3)
+        prev = L["last_leave"]
+    for kind, (n, us) in sorted(total.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {kind:18s} {n:4d} launches end {us:8.1f} us after the launch before them ended ({us / n:.2f} each)")
+    layers = cfg["num_hidden_layers"]
+    per_layer = (len(step) - 3) // layers if layers else 0
+    if per_layer:
+        layer = args.layer if args.layer is not None else layers // 2
+        first = 1 + per_layer * layer
+        base = prev = step[first - 1]["last_leave"]
+        print(f"layer {layer}, times in us after the launch in front of it ended ({per_layer} launches a layer):")
+        print("  kind               blocks  enter first..last   past the wait first..last   loads/scores issued   exit first..last   after the launch in front: go, end")
+        for L in step[first:first + per_layer]:
+            f = lambda v: f"{(v - base) / 1e3:7.2f}" if v else "      -"
+            print(f"  {L['kind']:18s} {L['blocks']:5d}  {f(L['first_enter'])} {f(L['last_enter'])}   {f(L['first_go'])} {f(L['last_go'])}"
+                  f"   {f(L['last_mark2'])}   {f(L['first_leave'])} {f(L['last_leave'])}   {(L['last_go'] - prev) / 1e3:6.2f} {(L['last_leave'] - prev) / 1e3:6.2f}")
+            prev = L["last_leave"]
     return 0
 
 
