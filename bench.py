@@ -314,7 +314,7 @@ def run_ours(args) -> dict:
         ms, launches, mean_ctx = decode_run(engine, BATCH, steps, warmup, seed=1, windows=windows)
         value = BATCH * 1000.0 / ms
         e2e, h2d, d2h = e2e_run(engine, BATCH, steps, seed=1, windows=windows)
-        pre_ms = prefill_run(engine, warmup=3, iters=5, seed=2, windows=windows)
+        pre_ms = prefill_run(engine, warmup=5, iters=15, seed=2, windows=windows)
         ms1, _, _ = decode_run(engine, 1, steps, warmup, seed=3, windows=windows)
         ms64, _, _ = decode_run(engine, 64, steps, warmup, seed=4, windows=windows)
         e2e1, _, _ = e2e_run(engine, 1, min(steps, 128), seed=3, windows=windows)
