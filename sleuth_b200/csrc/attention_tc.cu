@@ -778,6 +778,12 @@ extern "C" int slb_attention_tc_supported(int heads, int kv_heads, int head_dim)
   return (head_dim == 64 || head_dim == 128) && G <= 128 && (128 % G) == 0;
 }
 
+// 1 when a step of this shape would take the kernel that walks two pages a step (see wide_pays), else 0.
+extern "C" int slb_attention_tc_wide_pays(int n_seqs, int max_count, int max_keys, int heads, int kv_heads, int window) {
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || n_seqs <= 0 || max_count <= 0) return 0;
+  return wide_pays(n_seqs, max_count, max_keys, heads, kv_heads, window) ? 1 : 0;
+}
+
 // q [tokens, heads, head_dim]; k_pool, v_pool [pool_pages, kv_heads, 64, head_dim]; out [tokens, heads * head_dim];
 // all bfloat16. `status` is a zeroed device int that receives a code if a bounded wait inside the kernel gave up.
 // `wide`: 1 = the kernel that walks two pages a step, 0 = the one that walks one, -1 = chosen from the step's shape

@@ -196,6 +196,15 @@ def attention_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torc
     return head_dim in (64, 128) and group <= 128 and 128 % group == 0
 
 
+def attention_tc_takes_two_pages(n_seqs: int, max_count: int, max_keys: int, heads: int, kv_heads: int, window: int = 0) -> bool:
+    """Whether ``attention_tc``, left to choose, takes its kernel for long tiles (two pages a step, one block an SM)
+    for a step of ``n_seqs`` sequences whose longest brings ``max_count`` tokens and then has ``max_keys`` keys."""
+    fn = lib().dll.slb_attention_tc_wide_pays
+    fn.argtypes = [ctypes.c_int] * 6
+    fn.restype = ctypes.c_int
+    return fn(int(n_seqs), int(max_count), int(max_keys), int(heads), int(kv_heads), int(window)) != 0
+
+
 def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
                  kv_heads: int, head_dim: int, window: int, scale: float, stream=None, wide: bool | None = None,
                  max_keys: int = 0) -> None:

@@ -232,6 +232,17 @@ def test_attention_tcgen05_chooses_by_shape():
     run_attention("tc", bf, 16, 8, 128, pasts=[0] * 12, counts=[200] * 12, window=0, seed=8)       # many short tiles
 
 
+def test_attention_tcgen05_choice_follows_the_measurements():
+    """The shapes at which the two kernels were timed on a B200 (16 query heads, 8 kv heads), and which of them won."""
+    o = ops()
+    two = lambda n, count, past=0: o.attention_tc_takes_two_pages(n, count, past + count, 16, 8)
+    assert two(1, 256) and two(1, 512) and two(1, 1024) and two(1, 1536) and two(1, 2048)        # one round of blocks, or long tiles
+    assert not two(1, 3072) and not two(1, 4096) and not two(1, 8192)                              # several rounds
+    assert not two(8, 2048) and not two(16, 300) and not two(64, 100) and not two(4, 512)          # many tiles
+    assert two(1, 256, past=4096) and two(1, 512, past=8192)                                       # a chunk after a long past
+    assert not two(2, 1024, past=1024)
+
+
 def test_attention_tcgen05_growing_scores():
     """Scores that grow along the sequence force the running maximum up page after page, so the accumulator in
     tensor memory is rescaled many times; scores that shrink never rescale it. Both must agree with the reference."""
