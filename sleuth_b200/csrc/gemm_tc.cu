@@ -15,6 +15,9 @@
 //     the block then multiplies X by 128 gate rows and the 128 matching up rows in one N = 256 instruction.
 // Rows, columns and K beyond the matrices are zero-filled by TMA and masked at the store, so every M, N and every K
 // that is a multiple of 8 is taken. (The reference calls a library here: nn.Linear, sleuth/forge/model/attention.py:106-108.)
+// A lane of an epilogue warp holds a row of the tile, so epilogues move 32 bytes a lane where alignment allows (half as
+// many accesses of the load/store unit, which sets their length). With many rows (4,096 and more) two blocks of a
+// cluster share tiles of 256 rows through cta_group::2: see the template parameter PAIR below.
 //
 // Every wait is bounded: a thread that waits longer than a few seconds' worth of polls records where in
 // `status` and leaves its loop; the block then still frees its tensor memory and returns. TMA loads never use
