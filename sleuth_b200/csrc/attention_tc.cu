@@ -65,6 +65,46 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return y;
 }
 
+// The way a block's results leave (both kernels): a lane holds a row of the accumulator, so a warp's store would touch
+// 32 lines at once. The normalised rows go through shared memory instead, into the query tile's place (the last score
+// product has read it): rows of HD * 2 bytes, the 16-byte pieces of each 128 bytes exchanged by the row's low bits so
+// that a warp's 32 rows spread over the banks. stage_row writes COLS values of row r from column col0 on;
+// store_rows, after a barrier of the softmax warps, lets warp w of WARPS store 128 / WARPS rows, its lanes along a
+// row: whole 128-byte lines.
+template <int HD, int COLS>
+__device__ __forceinline__ void stage_row(uint32_t sQ, int r, int col0, const uint32_t (&o)[COLS], float inv) {
+#pragma unroll
+  for (int c = 0; c < COLS; c += 8) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+    const int piece = (col0 + c) >> 3;
+    const uint32_t dst = sQ + (uint32_t)(r * (HD * 2) + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h0)),
+                 "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
+                 "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
+  }
+}
+
+template <int HD, int WARPS>
+__device__ __forceinline__ void store_rows(uint32_t sQ, int w, int lane, int r0, int rows_total, bool ok, __nv_bfloat16* out,
+                                           int tok0, int G, int heads, int kh) {
+  constexpr int kPieces = HD / 8, kRowsAtOnce = 32 / kPieces, kRows = kAtRows / WARPS;
+  const int piece = lane % kPieces;
+#pragma unroll
+  for (int it = 0; it < kRows / kRowsAtOnce; ++it) {
+    const int rr = w * kRows + it * kRowsAtOnce + lane / kPieces;
+    const int Rr = r0 + rr;
+    if (ok && Rr < rows_total) {
+      const uint32_t src = sQ + (uint32_t)(rr * (HD * 2) + (((piece & ~7) | ((piece ^ rr) & 7)) << 4));
+      uint4 q;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(src) : "memory");
+      *reinterpret_cast<uint4*>(out + ((size_t)(tok0 + Rr / G) * heads + kh * G + Rr % G) * HD + piece * 8) = q;
+    }
+  }
+}
+
 template <int HD>
 struct AttnTcLayout {
   static constexpr int Q_BYTES = kAtRows * HD * 2;
@@ -346,36 +386,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
       for (int c0 = 0; c0 < HD / 2; c0 += 16) tmem_ld16_nowait(lane_addr + 128 + half * (HD / 2) + c0, o + c0);
       tmem_wait_ld();
-      // A lane holds a row, so a warp's store would touch 32 lines at once. The normalised rows go through shared
-      // memory instead, into the query tile's place (the last score product has read it): rows of HD * 2 bytes, the
-      // 16-byte pieces of each 128 bytes exchanged by the row's low bits so that a warp's 32 rows spread over the banks.
-#pragma unroll
-      for (int c = 0; c < HD / 2; c += 8) {
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-        const int piece = (half * (HD / 2) + c) >> 3;
-        const uint32_t dst = sQ + (uint32_t)(r * (HD * 2) + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h0)),
-                     "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
-                     "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
-      }
+      stage_row<HD, HD / 2>(sQ, r, half * (HD / 2), o, inv);
       asm volatile("bar.sync 5, 256;" ::: "memory");      // the eight softmax warps
-      // each warp stores sixteen rows, its lanes along a row: whole 128-byte lines
-      constexpr int kPieces = HD / 8, kRowsAtOnce = 32 / kPieces;
-      const int piece = lane % kPieces;
-#pragma unroll
-      for (int it = 0; it < 16 / kRowsAtOnce; ++it) {
-        const int rr = (warp - 2) * 16 + it * kRowsAtOnce + lane / kPieces;
-        const int Rr = r0 + rr;
-        if (ok && Rr < rows_total) {
-          const uint32_t src = sQ + (uint32_t)(rr * (HD * 2) + (((piece & ~7) | ((piece ^ rr) & 7)) << 4));
-          uint4 q;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(src) : "memory");
-          *reinterpret_cast<uint4*>(a.out + ((size_t)(tok0 + Rr / G) * a.heads + kh * G + Rr % G) * HD + piece * 8) = q;
-        }
-      }
+      store_rows<HD, 8>(sQ, warp - 2, lane, r0, rows_total, ok, a.out, tok0, G, a.heads, kh);
     }
   }
   tc_fence_before();
@@ -678,33 +691,9 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int c0 = 0; c0 < HD / 4; c0 += 16) tmem_ld16_nowait(lane_addr + 256 + part * (HD / 4) + c0, o + c0);
       tmem_wait_ld();
-      // through shared memory, as above: the query tile's place, 16-byte pieces exchanged by the row's low bits
-#pragma unroll
-      for (int c = 0; c < HD / 4; c += 8) {
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-        const int piece = (part * (HD / 4) + c) >> 3;
-        const uint32_t dst = sQ + (uint32_t)(r * (HD * 2) + (((piece & ~7) | ((piece ^ r) & 7)) << 4));
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(*reinterpret_cast<uint32_t*>(&h0)),
-                     "r"(*reinterpret_cast<uint32_t*>(&h1)), "r"(*reinterpret_cast<uint32_t*>(&h2)),
-                     "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
-      }
+      stage_row<HD, HD / 4>(sQ, r, part * (HD / 4), o, inv);
       asm volatile("bar.sync 5, 512;" ::: "memory");      // the sixteen softmax warps
-      constexpr int kPieces = HD / 8, kRowsAtOnce = 32 / kPieces;
-      const int piece = lane % kPieces;
-#pragma unroll
-      for (int it = 0; it < 8 / kRowsAtOnce; ++it) {
-        const int rr = (warp - 2) * 8 + it * kRowsAtOnce + lane / kPieces;
-        const int Rr = r0 + rr;
-        if (ok && Rr < rows_total) {
-          const uint32_t src = sQ + (uint32_t)(rr * (HD * 2) + (((piece & ~7) | ((piece ^ rr) & 7)) << 4));
-          uint4 q;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(src) : "memory");
-          *reinterpret_cast<uint4*>(a.out + ((size_t)(tok0 + Rr / G) * a.heads + kh * G + Rr % G) * HD + piece * 8) = q;
-        }
-      }
+      store_rows<HD, 16>(sQ, warp - 2, lane, r0, rows_total, ok, a.out, tok0, G, a.heads, kh);
     }
   }
   tc_fence_before();
