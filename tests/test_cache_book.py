@@ -33,7 +33,19 @@ def test_pool_take_give():
     p.give(a[:1])
     with pytest.raises(CacheMisuse):
         p.give(a[:1])
-    assert p.take(1) == a[:1]          # the page freed last is used again first
+    assert p.take(1) == a[:1]          # the lowest free page is used again first
+
+
+def test_pool_hands_out_the_lowest_pages_so_that_held_pages_stay_together():
+    p = PagePool(64)
+    first, second, third = p.take(10), p.take(10), p.take(10)
+    assert first == list(range(10)) and second == list(range(10, 20)) and third == list(range(20, 30))
+    p.give(second)
+    p.give(first[3:7])
+    # what comes back is used before untouched pages, in ascending order whatever the order of the returns
+    assert p.take(6) == [3, 4, 5, 6, 10, 11]
+    assert p.take(10) == [12, 13, 14, 15, 16, 17, 18, 19, 30, 31]
+    assert p.free == 64 - 32
 
 
 def test_slots_are_reused_and_lengths_start_at_zero():
